@@ -1,0 +1,42 @@
+// Host API of the tcgen05 bf16 GEMM family.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace z2h {
+
+// Epilogue selector.
+enum GemmEpilogue : int {
+  kEpiNone = 0,        // C = acc (+ bias)
+  kEpiResidual = 1,    // C = acc (+ bias) + residual
+  kEpiGelu = 2,        // aux_out = acc (+ bias);  C = gelu_tanh(aux_out)
+  kEpiGeluGrad = 3,    // C = acc * gelu_tanh'(aux_in)
+  kEpiAtomicAdd = 4,   // C(fp32) += acc with red.global.add (split-K capable)
+  kEpiAccumulate = 5,  // C(fp32) += acc with plain read-modify-write (deterministic)
+};
+
+// C[M,N] = A * B^T in the logical sense: A is M x K, B is N x K.
+// a_mn == 0: A is stored row-major [M, K] with pitch lda   (K-major)
+// a_mn == 1: A is stored row-major [K, M] with pitch lda   (MN-major, i.e. A^T in memory)
+// b_mn == 0: B is stored row-major [N, K] with pitch ldb   (K-major)
+// b_mn == 1: B is stored row-major [K, N] with pitch ldb   (MN-major)
+// All pitches are in elements and must be multiples of 8; base pointers 16-byte aligned.
+struct GemmArgs {
+  const void* A; int a_mn; long long lda;
+  const void* B; int b_mn; long long ldb;
+  void* C; long long ldc; int out_fp32;
+  int M, N, K;
+  int epi; int split_k;
+  const void* bias;       // bf16 [N] or null
+  const void* residual;   // bf16 [M, ldr]
+  long long ldr;
+  void* aux_out;          // bf16 [M, ldaux]
+  const void* aux_in;     // bf16 [M, ldaux]
+  long long ldaux;
+  int* status;            // device status word (0 == ok), may be null
+  int max_ctas;           // 0 = one CTA per SM
+};
+
+// Returns 0 on success, 1 bad argument, 2 tensor-map encoding failed, 3 launch failed.
+int gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+
+}  // namespace z2h

@@ -1,0 +1,485 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T with fp32
+// accumulation in tensor memory and a fused epilogue.
+//
+// One persistent CTA per SM walks a static tile schedule (M fastest, so the CTAs that run at
+// the same time share one B panel out of L2). Inside the CTA the work is split by warp role:
+//
+//   warp 0      TMA producer   cp.async.bulk.tensor 2-D tiles, 128-byte swizzle, 4-stage ring
+//   warp 1      MMA issuer     one elected lane issues tcgen05.mma (128x256x16) and commits
+//                              stage releases / accumulator completions to mbarriers
+//   warps 2-5   epilogue       tcgen05.ld the 128x256 fp32 accumulator (one row per thread),
+//                              apply bias / GELU / residual / GELU' and store
+//
+// Two accumulators of 256 TMEM columns each are used in turn, so the epilogue of tile i runs
+// while the tensor cores already work on tile i+1.
+//
+// Either operand may be K-major (the contraction index is contiguous in global memory) or
+// MN-major (the M / N index is contiguous); the second form is what the weight-gradient and
+// data-gradient GEMMs of a linear layer need, so no transposed copies are ever made.
+//
+// Replaces the nn.Linear calls of the reference model (nn/gpt2/modules.py:21-22,49-51,82) and
+// their autograd; the reference's own tensor-core kernel is gpu-mojo/problems/p33/p33.mojo:130-245.
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+#include "gemm.h"
+
+namespace z2h {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+
+struct KernelParams {
+  int M, N, K;
+  int split_k;
+  int epi;
+  int out_fp32;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* aux_out;
+  const __nv_bfloat16* aux_in;
+  long long ldaux;
+  int* status;
+};
+
+// Epilogue for 32 consecutive columns of one output row.
+__device__ __forceinline__ void epilogue_chunk(const KernelParams& p, float (&v)[32], long long grow,
+                                               int gcol) {
+  const int ncols = min(32, p.N - gcol);
+  if (ncols <= 0) return;
+  const bool full = (ncols == 32);
+  if (p.bias != nullptr) {
+    if (full) {
+      const uint4* bp = reinterpret_cast<const uint4*>(p.bias + gcol);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = __ldg(bp + q);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
+               f3 = unpack_bf16x2(b.w);
+        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+      }
+    } else {
+      #pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] += __bfloat162float(p.bias[gcol + j]);
+    }
+  }
+  if (p.epi == kEpiResidual) {
+    const __nv_bfloat16* rp = p.residual + grow * p.ldr + gcol;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = *reinterpret_cast<const uint4*>(rp + q * 8);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
+               f3 = unpack_bf16x2(b.w);
+        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+      }
+    } else {
+      #pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] += __bfloat162float(rp[j]);
+    }
+  } else if (p.epi == kEpiGelu) {
+    // keep the pre-activation for the backward pass, output the activation
+    __nv_bfloat16* ap = p.aux_out + grow * p.ldaux + gcol;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        *reinterpret_cast<uint4*>(ap + q * 8) = o;
+      }
+    } else {
+      #pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) ap[j] = __float2bfloat16(v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      // the activation is taken of the bf16-rounded pre-activation, as the backward pass sees it
+      float x = __bfloat162float(__float2bfloat16(v[j]));
+      v[j] = gelu_tanh(x);
+    }
+  } else if (p.epi == kEpiGeluGrad) {
+    const __nv_bfloat16* ap = p.aux_in + grow * p.ldaux + gcol;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = *reinterpret_cast<const uint4*>(ap + q * 8);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
+               f3 = unpack_bf16x2(b.w);
+        v[q * 8 + 0] *= gelu_tanh_grad(f0.x); v[q * 8 + 1] *= gelu_tanh_grad(f0.y);
+        v[q * 8 + 2] *= gelu_tanh_grad(f1.x); v[q * 8 + 3] *= gelu_tanh_grad(f1.y);
+        v[q * 8 + 4] *= gelu_tanh_grad(f2.x); v[q * 8 + 5] *= gelu_tanh_grad(f2.y);
+        v[q * 8 + 6] *= gelu_tanh_grad(f3.x); v[q * 8 + 7] *= gelu_tanh_grad(f3.y);
+      }
+    } else {
+      #pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] *= gelu_tanh_grad(__bfloat162float(ap[j]));
+    }
+  }
+
+  if (p.out_fp32) {
+    float* cp = reinterpret_cast<float*>(p.C) + grow * p.ldc + gcol;
+    if (p.epi == kEpiAtomicAdd) {
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4),
+                       "f"(v[q * 4 + 0]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                       : "memory");
+        }
+      } else {
+        #pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) atomicAdd(cp + j, v[j]);
+      }
+    } else if (p.epi == kEpiAccumulate) {
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 o = *reinterpret_cast<float4*>(cp + q * 4);
+          o.x += v[q * 4 + 0]; o.y += v[q * 4 + 1]; o.z += v[q * 4 + 2]; o.w += v[q * 4 + 3];
+          *reinterpret_cast<float4*>(cp + q * 4) = o;
+        }
+      } else {
+        #pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) cp[j] += v[j];
+      }
+    } else {
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          *reinterpret_cast<float4*>(cp + q * 4) =
+              make_float4(v[q * 4 + 0], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        }
+      } else {
+        #pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) cp[j] = v[j];
+      }
+    }
+  } else {
+    __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + gcol;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        *reinterpret_cast<uint4*>(cp + q * 8) = o;
+      }
+    } else {
+      #pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) cp[j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;
+  const int total_tiles = tiles_m * tiles_n * p.split_k;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mt = tile % tiles_m;
+        const int rest = tile / tiles_m;
+        const int nt = rest % tiles_n;
+        const int ks = rest / tiles_n;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                 kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (A_MN == 0) {
+            tma_load_2d(a_dst, &tmA, &full_bar[stage], kb * BK, mt * BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(a_dst + c * (64 * BK * 2), &tmA, &full_bar[stage], mt * BM + c * 64,
+                          kb * BK);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(b_dst, &tmB, &full_bar[stage], kb * BK, nt * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * (64 * BK * 2), &tmB, &full_bar[stage], nt * BN + c * 64,
+                          kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight a bounded time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t b_lbo = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int rest = tile / tiles_m;
+        const int ks = rest / tiles_n;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status,
+                               kTimeoutTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            tc_mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (4 warps) ------------------------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int mt = tile % tiles_m;
+      const int rest = tile / tiles_m;
+      const int nt = rest % tiles_n;
+      const int ks = rest / tiles_n;
+      const int kb0 = ks * kb_per_split;
+      const bool empty_split = kb0 >= num_kb_total;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long grow = (long long)mt * BM + row_in_tile;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+        tmem_ld_wait();
+        if (chunk == BN / 32 - 1) {
+          // the accumulator is in registers now: hand it back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        const int gcol = nt * BN + chunk * 32;
+        if (grow < p.M && gcol < p.N && !empty_split) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          epilogue_chunk(p, v, grow, gcol);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int A_MN, int B_MN>
+int launch(const GemmArgs& g, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (A_MN == 0)
+    ok = make_tma_2d_bf16(&tmA, g.A, g.M, g.K, g.lda, BM, BK, kSwizzle128);
+  else
+    ok = make_tma_2d_bf16(&tmA, g.A, g.K, g.M, g.lda, BK, 64, kSwizzle128);
+  if (!ok) return 2;
+  if (B_MN == 0)
+    ok = make_tma_2d_bf16(&tmB, g.B, g.N, g.K, g.ldb, BN, BK, kSwizzle128);
+  else
+    ok = make_tma_2d_bf16(&tmB, g.B, g.K, g.N, g.ldb, BK, 64, kSwizzle128);
+  if (!ok) return 2;
+
+  KernelParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.split_k = g.split_k < 1 ? 1 : g.split_k;
+  p.epi = g.epi;
+  p.out_fp32 = g.out_fp32;
+  p.C = g.C; p.ldc = g.ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(g.residual);
+  p.ldr = g.ldr;
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out);
+  p.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in);
+  p.ldaux = g.ldaux;
+  p.status = g.status;
+
+  static bool attr_set = false;
+  auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
+  static int num_sms = 0;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    attr_set = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * p.split_k;
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  if (grid < 1) return 0;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace
+
+int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
+  // argument checks: everything the TMA descriptors and the vector epilogue rely on
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15) ||
+      (reinterpret_cast<uintptr_t>(g.C) & 15))
+    return 1;
+  if ((g.lda % 8) || (g.ldb % 8) || (g.ldc % 8)) return 1;
+  if ((g.epi == kEpiAtomicAdd || g.epi == kEpiAccumulate) && !g.out_fp32) return 1;
+  if (g.split_k > 1 && g.epi != kEpiAtomicAdd) return 1;
+  if (g.epi == kEpiResidual && (g.residual == nullptr || (g.ldr % 8))) return 1;
+  if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
+  if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
+  if (g.a_mn == 0 && g.b_mn == 0) return launch<0, 0>(g, stream);
+  if (g.a_mn == 0 && g.b_mn == 1) return launch<0, 1>(g, stream);
+  if (g.a_mn == 1 && g.b_mn == 0) return launch<1, 0>(g, stream);
+  return launch<1, 1>(g, stream);
+}
+
+}  // namespace z2h
+
+extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                             long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                             int epi, int split_k, const void* bias, const void* residual,
+                             long long ldr, void* aux_out, const void* aux_in, long long ldaux,
+                             int* status, int max_ctas, void* stream) {
+  z2h::GemmArgs g;
+  g.A = A; g.a_mn = a_mn; g.lda = lda;
+  g.B = B; g.b_mn = b_mn; g.ldb = ldb;
+  g.C = C; g.ldc = ldc; g.out_fp32 = out_fp32;
+  g.M = M; g.N = N; g.K = K;
+  g.epi = epi; g.split_k = split_k;
+  g.bias = bias; g.residual = residual; g.ldr = ldr;
+  g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
+  g.status = status; g.max_ctas = max_ctas;
+  return z2h::gemm_bf16(g, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,285 @@
+// LayerNorm forward / backward over bf16 activations with fp32 statistics.
+//
+// forward : y = (x - mean) * rstd * w (+ b); one warp per row, the row is read once with
+//           16-byte loads and kept in registers; mean / rstd are saved for the backward pass.
+// backward: dx = dresid + rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * w
+//           dw += sum_rows dy * xhat,  db += sum_rows dy
+//           The weight/bias gradients are reduced without atomics in two stages: every CTA
+//           sums its rows per column and writes one partial row to a scratch buffer
+//           [num_ctas, 2, C]; a second kernel folds the partials in a fixed order and adds the
+//           result to the fp32 gradient, so the result does not depend on scheduling.
+//
+// Semantics follow nn.LayerNorm(bias=False) of the reference model (nn/gpt2/modules.py:62-69,81)
+// and the hand-written weight+bias LayerNorm of the char-level model (nn/gpt/3_gpt.py:79-91):
+// biased variance, eps inside the square root.
+#include "../common/ptx.cuh"
+#include "norm.h"
+
+namespace z2h {
+namespace {
+
+constexpr int kMaxVec = 8;  // per-lane 8-element vectors: rows up to 32 * 8 * 8 = 2048 wide
+constexpr int kWarpsPerCta = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+         d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <int NVEC>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                     const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int C,
+                     float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + warp;
+  if (row >= M) return;
+  const __nv_bfloat16* xr = x + (long long)row * C;
+  float v[NVEC][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+      load8(xr + c, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+  }
+  const float mean = warp_sum(s) / C;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float d = v[i][j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / C + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + (long long)row * C;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+      float wv[8], o[8];
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * wv[j];
+      if (b != nullptr) {
+        float bv[8];
+        load8(b + c, bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += bv[j];
+      }
+      store8(yr + c, o);
+    }
+  }
+}
+
+// scratch layout: [gridDim.x][2][C] fp32 (dw partials, then db partials)
+template <int NVEC, bool HAS_DB>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, int M, int C) {
+  extern __shared__ float sh[];  // [kWarpsPerCta][2][C]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float dw_acc[NVEC][8];
+  float db_acc[HAS_DB ? NVEC : 1][8];
+  uint4 wraw[NVEC];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    wraw[i] = make_uint4(0, 0, 0, 0);
+    if (c < C) wraw[i] = *reinterpret_cast<const uint4*>(w + c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dw_acc[i][j] = 0.f;
+      if (HAS_DB) db_acc[i][j] = 0.f;
+    }
+  }
+  for (int row = blockIdx.x * kWarpsPerCta + warp; row < M; row += gridDim.x * kWarpsPerCta) {
+    const long long off = (long long)row * C;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    uint4 dyraw[NVEC], xraw[NVEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        dyraw[i] = *reinterpret_cast<const uint4*>(dy + off + c);
+        xraw[i] = *reinterpret_cast<const uint4*>(x + off + c);
+        const uint32_t* dyu = reinterpret_cast<const uint32_t*>(&dyraw[i]);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xraw[i]);
+        const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 d = unpack_bf16x2(dyu[j]), xv = unpack_bf16x2(xu[j]), wv = unpack_bf16x2(wu[j]);
+          float xh0 = (xv.x - mean) * rstd, xh1 = (xv.y - mean) * rstd;
+          float g0 = d.x * wv.x, g1 = d.y * wv.y;
+          s1 += g0 + g1;
+          s2 += g0 * xh0 + g1 * xh1;
+          dw_acc[i][2 * j] += d.x * xh0;
+          dw_acc[i][2 * j + 1] += d.y * xh1;
+          if (HAS_DB) {
+            db_acc[i][2 * j] += d.x;
+            db_acc[i][2 * j + 1] += d.y;
+          }
+        }
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        const uint32_t* dyu = reinterpret_cast<const uint32_t*>(&dyraw[i]);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xraw[i]);
+        const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw[i]);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 d = unpack_bf16x2(dyu[j]), xv = unpack_bf16x2(xu[j]), wv = unpack_bf16x2(wu[j]);
+          float xh0 = (xv.x - mean) * rstd, xh1 = (xv.y - mean) * rstd;
+          o[2 * j] = rstd * (d.x * wv.x - s1 - xh0 * s2);
+          o[2 * j + 1] = rstd * (d.y * wv.y - s1 - xh1 * s2);
+        }
+        if (dresid != nullptr) {
+          float r[8];
+          load8(dresid + off + c, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dx + off + c, o);
+      }
+    }
+  }
+  // fold the 8 warps of this CTA, then write one partial row
+  float* my = sh + warp * 2 * C;
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        my[c + j] = dw_acc[i][j];
+        my[C + c + j] = HAS_DB ? db_acc[i][j] : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarpsPerCta; ++wi) t += sh[wi * 2 * C + c];
+    scratch[(long long)blockIdx.x * 2 * C + c] = t;
+  }
+}
+
+__global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int num_partials,
+                                            float* __restrict__ dw, float* __restrict__ db, int C,
+                                            int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float sw = 0.f, sb = 0.f;
+  for (int p = 0; p < num_partials; ++p) {
+    sw += scratch[(long long)p * 2 * C + c];
+    sb += scratch[(long long)p * 2 * C + C + c];
+  }
+  if (dw != nullptr) dw[c] = accumulate ? dw[c] + sw : sw;
+  if (db != nullptr) db[c] = accumulate ? db[c] + sb : sb;
+}
+
+}  // namespace
+
+int layernorm_bwd_num_partials(int M) {
+  int rows_ctas = (M + kWarpsPerCta - 1) / kWarpsPerCta;
+  return rows_ctas < kLayerNormBwdMaxCtas ? rows_ctas : kLayerNormBwdMaxCtas;
+}
+
+int layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                  int M, int C, float eps, cudaStream_t stream) {
+  if (C % 8 != 0 || C > 32 * 8 * kMaxVec) return 1;
+  if (M <= 0) return 0;
+  const int grid = (M + kWarpsPerCta - 1) / kWarpsPerCta;
+#define Z2H_LN_FWD(NV)                                                                         \
+  layernorm_fwd_kernel<NV><<<grid, kWarpsPerCta * 32, 0, stream>>>(                             \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, \
+      mean, rstd, M, C, eps)
+  if (C <= 768) Z2H_LN_FWD(3);
+  else if (C <= 1024) Z2H_LN_FWD(4);
+  else Z2H_LN_FWD(8);
+#undef Z2H_LN_FWD
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                  const void* dresid, void* dx, float* dw, float* db, float* scratch, int M, int C,
+                  int accumulate, cudaStream_t stream) {
+  if (C % 8 != 0 || C > 32 * 8 * kMaxVec) return 1;
+  if (M <= 0) return 0;
+  const int grid = layernorm_bwd_num_partials(M);
+  const size_t smem = (size_t)kWarpsPerCta * 2 * C * sizeof(float);
+#define Z2H_LN_BWD(NV, DB)                                                                     \
+  do {                                                                                         \
+    auto kern = layernorm_bwd_kernel<NV, DB>;                                                  \
+    static bool attr = false;                                                                  \
+    if (!attr) {                                                                               \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                           kWarpsPerCta * 2 * 32 * 8 * NV * (int)sizeof(float));               \
+      attr = true;                                                                             \
+    }                                                                                          \
+    kern<<<grid, kWarpsPerCta * 32, smem, stream>>>(                                           \
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, rstd, \
+        (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, M, C);                      \
+  } while (0)
+  const bool has_db = db != nullptr;
+  if (C <= 768) { if (has_db) Z2H_LN_BWD(3, true); else Z2H_LN_BWD(3, false); }
+  else if (C <= 1024) { if (has_db) Z2H_LN_BWD(4, true); else Z2H_LN_BWD(4, false); }
+  else { if (has_db) Z2H_LN_BWD(8, true); else Z2H_LN_BWD(8, false); }
+#undef Z2H_LN_BWD
+  layernorm_bwd_reduce_kernel<<<(C + 255) / 256, 256, 0, stream>>>(scratch, grid, dw, db, C,
+                                                                 accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace z2h
+
+extern "C" {
+int z2h_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                      int M, int C, float eps, void* stream) {
+  return z2h::layernorm_fwd(x, w, b, y, mean, rstd, M, C, eps, (cudaStream_t)stream);
+}
+int z2h_layernorm_bwd_num_partials(int M) { return z2h::layernorm_bwd_num_partials(M); }
+int z2h_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                      const float* rstd, const void* dresid, void* dx, float* dw, float* db,
+                      float* scratch, int M, int C, int accumulate, void* stream) {
+  return z2h::layernorm_bwd(dy, x, w, mean, rstd, dresid, dx, dw, db, scratch, M, C, accumulate,
+                            (cudaStream_t)stream);
+}
+}

@@ -1,0 +1,112 @@
+"""In-tree build of the native libraries.
+
+`build_all()` compiles every `.cu` / `.cpp` under `csrc/` for sm_100a with nvcc and links
+`zero_to_hero_b200/lib/libz2h.so` (CUDA kernels + C ABI) and `libz2h_host.so` (host-only C++:
+micrograd engine, CPU oracles). nvcc cross-compiles without a GPU, so this also is the
+"does it build" check. Objects are cached under `build/` keyed on source mtimes.
+
+Run as `python -m zero_to_hero_b200.build [--force] [--verbose]`.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+LIBDIR = Path(__file__).resolve().parent / "lib"
+OBJDIR = ROOT / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=default",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
+
+
+def _headers_stamp() -> str:
+    h = hashlib.sha1()
+    for p in sorted(list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.hpp"))):
+        h.update(str(p).encode())
+        h.update(str(p.stat().st_mtime_ns).encode())
+    return h.hexdigest()[:12]
+
+
+def _compile(src: Path, obj: Path, cmd: list[str], verbose: bool) -> tuple[Path, str]:
+    obj.parent.mkdir(parents=True, exist_ok=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(r.stderr, file=sys.stderr)
+    return obj, r.stderr
+
+
+def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
+    """Compile all native sources; returns {'cuda': path, 'host': path}."""
+    nvcc = _nvcc()
+    stamp = _headers_stamp()
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    cu_srcs = sorted(p for p in CSRC.rglob("*.cu"))
+    host_srcs = sorted(p for p in (CSRC / "cpu").rglob("*.cpp"))
+    jobs = []
+    cu_objs, host_objs = [], []
+    for src in cu_srcs:
+        rel = src.relative_to(CSRC)
+        obj = OBJDIR / rel.with_suffix(f".{stamp}.o")
+        cu_objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime_ns < src.stat().st_mtime_ns:
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append((src, obj, cmd))
+    for src in host_srcs:
+        rel = src.relative_to(CSRC)
+        obj = OBJDIR / rel.with_suffix(f".{stamp}.o")
+        host_objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime_ns < src.stat().st_mtime_ns:
+            cmd = ["g++", *CXX_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            jobs.append((src, obj, cmd))
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            futs = [ex.submit(_compile, s, o, c, verbose) for s, o, c in jobs]
+            for f in futs:
+                f.result()
+    out = {}
+    cuda_lib = LIBDIR / "libz2h.so"
+    if cu_objs and (jobs or force or not cuda_lib.exists()):
+        cmd = [nvcc, "-shared", "-o", str(cuda_lib), *map(str, cu_objs),
+               "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {r.stderr}")
+    out["cuda"] = cuda_lib
+    host_lib = LIBDIR / "libz2h_host.so"
+    if host_objs and (jobs or force or not host_lib.exists()):
+        cmd = ["g++", "-shared", "-o", str(host_lib), *map(str, host_objs), "-pthread"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {r.stderr}")
+    out["host"] = host_lib
+    return out
+
+
+if __name__ == "__main__":
+    libs = build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    for k, v in libs.items():
+        print(f"{k}: {v} ({v.stat().st_size if v.exists() else 0} bytes)")

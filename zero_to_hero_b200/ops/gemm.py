@@ -1,0 +1,60 @@
+"""Python entry to the tcgen05 bf16 GEMM family (csrc/gemm/gemm_tcgen05.cu)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+EPI_NONE, EPI_RESIDUAL, EPI_GELU, EPI_GELU_GRAD, EPI_ATOMIC_ADD, EPI_ACCUMULATE = range(6)
+
+_configured = False
+
+
+def _fn():
+    global _configured
+    lib = _lib.cuda_lib()
+    if not _configured:
+        lib.z2h_gemm_bf16.restype = ctypes.c_int
+        lib.z2h_gemm_bf16.argtypes = [
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
+            ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
+            ctypes.c_int, ctypes.c_int, ctypes.c_int,
+            ctypes.c_int, ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+        ]
+        _configured = True
+    return lib.z2h_gemm_bf16
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False,
+         b_mn: bool = False, epi: int = EPI_NONE, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, aux_out: torch.Tensor | None = None,
+         aux_in: torch.Tensor | None = None, split_k: int = 1, max_ctas: int = 0) -> torch.Tensor:
+    """out[M,N] (op)= A · Bᵀ on the tensor cores.
+
+    `a` is [M,K] (or [K,M] when `a_mn`), `b` is [N,K] (or [K,N] when `b_mn`); both bf16 with a
+    unit inner stride. `out` is bf16 or fp32 [M,N]. See csrc/gemm/gemm.h for the epilogues.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    assert (a.shape[1] if a_mn else a.shape[0]) == M, (a.shape, out.shape, a_mn)
+    assert (b.shape[1] if b_mn else b.shape[0]) == N, (b.shape, out.shape, b_mn)
+    assert (b.shape[0] if b_mn else b.shape[1]) == K
+    out_fp32 = out.dtype == torch.float32
+    aux = aux_out if aux_out is not None else aux_in
+    rc = _fn()(
+        _lib.ptr(a), int(a_mn), a.stride(0), _lib.ptr(b), int(b_mn), b.stride(0),
+        _lib.ptr(out), out.stride(0), int(out_fp32), M, N, K, epi, split_k,
+        _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+        _lib.ptr(aux_out), _lib.ptr(aux_in), aux.stride(0) if aux is not None else 0,
+        _lib.ptr(_lib.status_word(out.device)), max_ctas, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"z2h_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
+    return out
