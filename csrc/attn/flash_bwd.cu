@@ -1,0 +1,428 @@
+// Causal flash attention backward, head_dim 64, bf16, on tcgen05 tensor cores.
+//
+// One CTA owns one KV tile (128 keys of one batch/head) and walks the query tiles from the
+// diagonal to the end of the sequence. All five products of the backward run on the tensor
+// cores, with the "transposed" formulation so that a thread owns one key row:
+//
+//   S^T  = K  Q^T          (128 x 128 x 64)    TMEM cols   0..127
+//   dP^T = V  dO^T         (128 x 128 x 64)    TMEM cols 128..255
+//   P^T  = exp(S^T * scale - lse),  dS^T = P^T o (dP^T - delta)        (threads, fp32)
+//   dV  += P^T  dO         (128 x 64 x 128)    TMEM cols 256..319, accumulated over q tiles
+//   dK  += dS^T Q          (128 x 64 x 128)    TMEM cols 320..383, accumulated over q tiles
+//   dQ_i = dS K            (128 x 64 x 128)    TMEM cols 384..447, added to an fp32 buffer
+//
+// P^T and dS^T are written once to swizzled shared memory as bf16 and are consumed as the
+// K-major A operand of the dV / dK products and as the MN-major A operand of the dQ product;
+// Q, dO and K tiles serve as K-major or MN-major B operands straight from their TMA tiles, so
+// nothing is transposed in memory. dQ contributions of different KV tiles meet in an fp32
+// accumulation buffer (vector red.global.add), which a small kernel scales and converts.
+//
+// This is the hand-written counterpart of what autograd runs for
+// F.scaled_dot_product_attention in the reference (nn/gpt2/modules.py:37, train_ddp.py:141).
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+#include "attn.h"
+
+namespace z2h {
+namespace {
+
+constexpr int TS = 128;  // tile size (queries and keys)
+constexpr int HD = 64;
+constexpr int TILE_BYTES = TS * HD * 2;  // 16 KiB
+constexpr int PT_BYTES = TS * TS * 2;    // 32 KiB
+constexpr int Q_STAGES = 2;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384;
+constexpr int SMEM_BYTES =
+    1024 + 2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + 2 * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  __nv_bfloat16* dqkv;
+  float* dq_accum;
+  int B, T, H, C;
+  float scale, scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                 const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;
+  uint8_t* sdO = sQ + Q_STAGES * TILE_BYTES;
+  uint8_t* sPt = sdO + Q_STAGES * TILE_BYTES;
+  uint8_t* sdSt = sPt + PT_BYTES;
+  float* sLse = reinterpret_cast<float*>(sdSt + PT_BYTES);  // [Q_STAGES][TS], already * log2(e)
+  float* sDelta = sLse + Q_STAGES * TS;                      // [Q_STAGES][TS]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + Q_STAGES * TS);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = qdo_full + Q_STAGES;
+  uint64_t* st_full = qdo_empty + Q_STAGES;
+  uint64_t* pds_full = st_full + 1;
+  uint64_t* dq_full = pds_full + 1;
+  uint64_t* stat_full = dq_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = (p.T + TS - 1) / TS;
+  // KV tile 0 has the most query tiles to visit: schedule it first
+  const int j = (int)(blockIdx.x % n_t);
+  const int bh = blockIdx.x / n_t;
+  const int h = bh % p.H, b = bh / p.H;
+  const int row0 = b * p.T;
+  const int n_iter = n_t - j;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < Q_STAGES; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(st_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(stat_full, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_2d(sK, &tm_qkv, kv_full, p.C + h * HD, row0 + j * TS);
+      tma_load_2d(sV, &tm_qkv, kv_full, 2 * p.C + h * HD, row0 + j * TS);
+      for (int it = 0; it < n_iter; ++it) {
+        const int i = j + it;
+        const int s = it % Q_STAGES;
+        const uint32_t ph = (it / Q_STAGES) & 1;
+        if (!mbar_wait_bounded(&qdo_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_arrive_expect_tx(&qdo_full[s], 2 * TILE_BYTES);
+        tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &qdo_full[s], h * HD, row0 + i * TS);
+        tma_load_2d(sdO + s * TILE_BYTES, &tm_do, &qdo_full[s], h * HD, row0 + i * TS);
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(TS, TS, 0, 0);
+      constexpr uint32_t idesc_dvk = make_idesc_bf16(TS, HD, 0, 1);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(TS, HD, 1, 1);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      const uint32_t pt_addr = smem_u32(sPt), dst_addr = smem_u32(sdSt);
+      auto issue_st = [&](int s) {
+        const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          tc_mma_f16_ss(tmem_base + ST_COL, make_smem_desc_sw128(k_addr + k * 32, 16, 1024),
+                        make_smem_desc_sw128(q_addr + k * 32, 16, 1024), idesc_st, k > 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          tc_mma_f16_ss(tmem_base + DPT_COL, make_smem_desc_sw128(v_addr + k * 32, 16, 1024),
+                        make_smem_desc_sw128(do_addr + k * 32, 16, 1024), idesc_st, k > 0);
+        tc_commit(st_full);
+      };
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) ok = mbar_wait_bounded(&qdo_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) {
+        tc_fence_after();
+        issue_st(0);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % Q_STAGES;
+        if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + DV_COL, make_smem_desc_sw128(pt_addr + a_off, 16, 1024),
+                        make_smem_desc_sw128(do_addr + k * 2048, 16, 1024), idesc_dvk,
+                        (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + DK_COL, make_smem_desc_sw128(dst_addr + a_off, 16, 1024),
+                        make_smem_desc_sw128(q_addr + k * 2048, 16, 1024), idesc_dvk,
+                        (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          tc_mma_f16_ss(tmem_base + DQ_COL,
+                        make_smem_desc_sw128(dst_addr + k * 2048, TS * 128, 1024),
+                        make_smem_desc_sw128(k_addr + k * 2048, 16, 1024), idesc_dq, k > 0);
+        }
+        tc_commit(dq_full);
+        tc_commit(&qdo_empty[s]);
+        if (it + 1 < n_iter) {
+          const int s2 = (it + 1) % Q_STAGES;
+          const uint32_t ph2 = ((it + 1) / Q_STAGES) & 1;
+          if (!mbar_wait_bounded(&qdo_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
+          tc_fence_after();
+          issue_st(s2);
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // key row (S^T, dV, dK) or query row (dQ) == TMEM lane
+    const int ct = threadIdx.x - 64;    // 0..127 among the compute threads
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const uint32_t pt_row = smem_u32(sPt) + r * 128;
+    const uint32_t dst_row = smem_u32(sdSt) + r * 128;
+    const long long stat_base = ((long long)b * p.H + h) * p.T;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int i = j + it;
+      const int s = it % Q_STAGES;
+      // stage the per-query statistics of this q tile (one value per compute thread)
+      {
+        const int t = i * TS + ct;
+        sLse[s * TS + ct] = t < p.T ? p.lse[stat_base + t] * 1.4426950408889634f : 0.f;
+        sDelta[s * TS + ct] = t < p.T ? p.delta[stat_base + t] : 0.f;
+      }
+      mbar_arrive(stat_full);
+      if (!mbar_wait_bounded(stat_full, it & 1, abort_flag, p.status, kTimeoutLocal)) {
+        ok = false;
+        break;
+      }
+      if (!mbar_wait_bounded(st_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool diag = (i == j);
+      const int q_valid = p.T - i * TS;  // columns >= q_valid are past the end of the sequence
+      const float* lse2 = sLse + s * TS;
+      const float* dlt = sDelta + s * TS;
+#pragma unroll 1
+      for (int ch = 0; ch < TS / 32; ++ch) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(t_lane + ST_COL + ch * 32, sv);
+        tmem_ld_32x32b_x32(t_lane + DPT_COL + ch * 32, dv);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int c0 = ch * 32 + e, c1 = c0 + 1;
+          float p0 = exp2f(__uint_as_float(sv[e]) * p.scale_log2 - lse2[c0]);
+          float p1 = exp2f(__uint_as_float(sv[e + 1]) * p.scale_log2 - lse2[c1]);
+          if ((diag && c0 < r) || c0 >= q_valid) p0 = 0.f;
+          if ((diag && c1 < r) || c1 >= q_valid) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dv[e]) - dlt[c0]);
+          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dlt[c1]);
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+          dk[e >> 1] = pack_bf16x2(d0, d1);
+        }
+        const uint32_t atom_off = (ch >> 1) * (TS * 128);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t chunk = ((uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7)) * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + atom_off + chunk),
+                       "r"(pk[q * 4 + 0]), "r"(pk[q * 4 + 1]), "r"(pk[q * 4 + 2]), "r"(pk[q * 4 + 3])
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + atom_off + chunk),
+                       "r"(dk[q * 4 + 0]), "r"(dk[q * 4 + 1]), "r"(dk[q * 4 + 2]), "r"(dk[q * 4 + 3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      if (!mbar_wait_bounded(dq_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // dQ tile: TMEM lane == query row of tile i
+      const int tq = i * TS + r;
+      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD;
+#pragma unroll
+      for (int ch = 0; ch < HD / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + DQ_COL + ch * 32, v);
+        tmem_ld_wait();
+        if (tq < p.T) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + ch * 32 + q * 4),
+                         "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
+                         "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
+                         : "memory");
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    // dV and dK of this KV tile are complete once the last dq_full has fired
+    const int tk = j * TS + r;
+    if (ok) {
+      __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD;
+      __nv_bfloat16* dv_row = dk_row + p.C;
+#pragma unroll
+      for (int ch = 0; ch < HD / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + DV_COL + ch * 32, v);
+        tmem_ld_wait();
+        if (tk < p.T) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+            u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+            u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+            u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+            *reinterpret_cast<uint4*>(dv_row + ch * 32 + q * 8) = u;
+          }
+        }
+        tmem_ld_32x32b_x32(t_lane + DK_COL + ch * 32, v);
+        tmem_ld_wait();
+        if (tk < p.T) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]) * p.scale, __uint_as_float(v[q * 8 + 1]) * p.scale);
+            u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]) * p.scale, __uint_as_float(v[q * 8 + 3]) * p.scale);
+            u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]) * p.scale, __uint_as_float(v[q * 8 + 5]) * p.scale);
+            u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]) * p.scale, __uint_as_float(v[q * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(dk_row + ch * 32 + q * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; also clears the fp32 dQ rows.
+__global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
+                                      const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                      float* __restrict__ dq_accum, int B, int T, int H) {
+  const long long total = (long long)B * T * H;
+  const int C = H * HD;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int hh = (int)(idx % H);
+    const long long m = idx / H;
+    const __nv_bfloat16* o = out + m * C + hh * HD;
+    const __nv_bfloat16* d = dout + m * C + hh * HD;
+    float* dq = dq_accum + m * C + hh * HD;
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < HD / 8; ++q) {
+      uint4 a = *reinterpret_cast<const uint4*>(o + q * 8);
+      uint4 c = *reinterpret_cast<const uint4*>(d + q * 8);
+      const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* cw = reinterpret_cast<const uint32_t*>(&c);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 x = unpack_bf16x2(aw[e]), y = unpack_bf16x2(cw[e]);
+        s += x.x * y.x + x.y * y.y;
+      }
+      reinterpret_cast<float4*>(dq)[q * 2] = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(dq)[q * 2 + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int bb = (int)(m / T), t = (int)(m % T);
+    delta[((long long)bb * H + hh) * T + t] = s;
+  }
+}
+
+// dqkv[m, 0:C] = bf16(dq_accum[m, :] * scale)
+__global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
+                                            __nv_bfloat16* __restrict__ dqkv, long long M, int C,
+                                            float scale) {
+  const int vec_per_row = C / 8;
+  const long long total = M * vec_per_row;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long m = idx / vec_per_row;
+    const int c = (int)(idx % vec_per_row) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(dq_accum + m * C + c);
+    const float4 b2 = *reinterpret_cast<const float4*>(dq_accum + m * C + c + 4);
+    uint4 u;
+    u.x = pack_bf16x2(a.x * scale, a.y * scale);
+    u.y = pack_bf16x2(a.z * scale, a.w * scale);
+    u.z = pack_bf16x2(b2.x * scale, b2.y * scale);
+    u.w = pack_bf16x2(b2.z * scale, b2.w * scale);
+    *reinterpret_cast<uint4*>(dqkv + m * 3 * C + c) = u;
+  }
+}
+
+}  // namespace
+
+int flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+              float* dq_accum, float* delta, int B, int T, int H, int* status, cudaStream_t stream) {
+  const int C = H * HD;
+  if (B <= 0 || T <= 0) return 0;
+  CUtensorMap tm_qkv, tm_do;
+  if (!make_tma_2d_bf16(&tm_qkv, qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, HD, kSwizzle128)) return 2;
+  if (!make_tma_2d_bf16(&tm_do, dout, (uint64_t)B * T, C, C, 128, HD, kSwizzle128)) return 2;
+  {
+    const long long total = (long long)B * T * H;
+    const int grid = (int)((total + 255) / 256);
+    flash_bwd_prep_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
+                                                  delta, dq_accum, B, T, H);
+  }
+  BwdParams p;
+  p.lse = lse; p.delta = delta;
+  p.dqkv = (__nv_bfloat16*)dqkv;
+  p.dq_accum = dq_accum;
+  p.B = B; p.T = T; p.H = H; p.C = C;
+  p.scale = 0.125f;
+  p.scale_log2 = 0.125f * 1.4426950408889634f;
+  p.status = status;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    attr = true;
+  }
+  const int n_t = (T + TS - 1) / TS;
+  flash_bwd_kernel<<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
+  {
+    const long long total = (long long)B * T * (C / 8);
+    const int grid = (int)((total + 255) / 256);
+    flash_bwd_dq_convert_kernel<<<grid, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dqkv,
+                                                        (long long)B * T, C, 0.125f);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace z2h
+
+extern "C" int z2h_flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
+                             void* dqkv, float* dq_accum, float* delta, int B, int T, int H,
+                             int* status, void* stream) {
+  return z2h::flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, delta, B, T, H, status,
+                        (cudaStream_t)stream);
+}

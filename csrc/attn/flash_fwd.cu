@@ -1,0 +1,299 @@
+// Causal flash attention forward, head_dim 64, bf16, on tcgen05 tensor cores.
+//
+// Input is the fused projection output qkv[B*T, 3*C] (q | k | v, head h in columns h*64..),
+// exactly what the QKV GEMM writes; output is out[B*T, C] with heads already merged, so the
+// split / transpose / contiguous copies of the reference (nn/gpt2/modules.py:31-39) never
+// happen. The softmax scale is 1/sqrt(64), masking is causal, as in
+// F.scaled_dot_product_attention(q, k, v, is_causal=True) (nn/gpt2/modules.py:37).
+//
+// One CTA handles 128 query rows of one (batch, head) and walks the KV tiles 0..diagonal:
+//   warp 0     TMA: Q once, K/V tiles through a 2-stage ring (128-byte swizzle)
+//   warp 1     tcgen05.mma: S = Q K^T (128x128x64) into TMEM, then O_j = P V (128x64x128)
+//   warps 2-5  one query row per thread: read S from TMEM, online softmax in fp32 (no
+//              shuffles: a thread owns its row), write P as bf16 into swizzled shared memory
+//              for the second MMA, then fold O_j into the register accumulator.
+// TMEM use is 192 columns (allocated as 256) and shared memory ~113 KiB, so two CTAs share an
+// SM and one CTA's tensor-core work overlaps the other's exponentials.
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+#include "attn.h"
+
+namespace z2h {
+namespace {
+
+constexpr int QT = 128;   // query rows per CTA
+constexpr int KT = 128;   // kv rows per tile
+constexpr int HD = 64;
+constexpr int TILE_BYTES = 128 * HD * 2;  // 16 KiB
+constexpr int P_BYTES = QT * KT * 2;      // 32 KiB
+constexpr int KV_STAGES = 2;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 256;
+constexpr int S_COL = 0, PV_COL = 128;
+// two CTAs per SM need (dynamic + 1 KiB reserved) * 2 <= 228 KiB, i.e. at most 115,712 bytes each
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 256;
+static_assert(SMEM_BYTES <= 115712, "two CTAs per SM no longer fit");
+
+struct FwdParams {
+  __nv_bfloat16* out;
+  float* lse;
+  int B, T, H, C;
+  float scale_log2;  // softmax_scale * log2(e)
+  float scale;
+  int* status;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (smem_u32(smem_raw) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
+    return;
+  }
+  uint8_t* sQ = smem_raw;
+  uint8_t* sK = sQ + TILE_BYTES;
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
+  uint8_t* sP = sV + KV_STAGES * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = k_full + KV_STAGES;
+  uint64_t* kv_empty = v_full + KV_STAGES;
+  uint64_t* s_full = kv_empty + KV_STAGES;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* pv_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.T + QT - 1) / QT;
+  // heavy (late) query tiles first
+  const int qi = n_qt - 1 - (int)(blockIdx.x % n_qt);
+  const int bh = blockIdx.x / n_qt;
+  const int h = bh % p.H, b = bh / p.H;
+  const int n_kv = qi + 1;
+  const int row0 = b * p.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(pv_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(sQ, &tm_qkv, q_full, h * HD, row0 + qi * QT);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+        tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &k_full[s], p.C + h * HD, row0 + j * KT);
+        mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+        tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &v_full[s], 2 * p.C + h * HD, row0 + j * KT);
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(QT, KT, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(QT, HD, 0, 1);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) ok = mbar_wait_bounded(&k_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          tc_mma_f16_ss(tmem_base + S_COL, make_smem_desc_sw128(q_addr + k * 32, 16, 1024),
+                        make_smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+        tc_commit(s_full);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        if (!mbar_wait_bounded(&v_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < KT / 16; ++k) {
+          const uint32_t pa = p_addr + (k >> 2) * (QT * 128) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + PV_COL, make_smem_desc_sw128(pa, 16, 1024),
+                        make_smem_desc_sw128(v_addr + k * 2048, 16, 1024), idesc_pv, k > 0);
+        }
+        tc_commit(pv_full);
+        tc_commit(&kv_empty[s]);
+        if (j + 1 < n_kv) {
+          const int s2 = (j + 1) % KV_STAGES;
+          const uint32_t ph2 = ((j + 1) / KV_STAGES) & 1;
+          if (!mbar_wait_bounded(&k_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sK + s2 * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k)
+            tc_mma_f16_ss(tmem_base + S_COL, make_smem_desc_sw128(q_addr + k * 32, 16, 1024),
+                          make_smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+          tc_commit(s_full);
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // query row within the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    const uint32_t p_row = smem_u32(sP) + r * 128;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait_bounded(s_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool diag = (j == qi);
+      float m_new = m_run;
+#pragma unroll 1
+      for (int ch = 0; ch < KT / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = __uint_as_float(v[i]);
+          if (!diag || ch * 32 + i <= r) m_new = fmaxf(m_new, x);
+        }
+      }
+      const float mc = m_new * p.scale_log2;
+      const float alpha = exp2f(m_run * p.scale_log2 - mc);  // exp2(-inf) == 0 on the first tile
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < KT / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - mc);
+          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - mc);
+          if (diag) {
+            if (ch * 32 + i > r) p0 = 0.f;
+            if (ch * 32 + i + 1 > r) p1 = 0.f;
+          }
+          rowsum += p0 + p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        // 32 columns = four 16-byte chunks of this row inside swizzle atom (ch >> 1)
+        const uint32_t atom = p_row + (ch >> 1) * (QT * 128);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t chunk = (uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(atom + chunk * 16),
+                       "r"(pk[q * 4 + 0]), "r"(pk[q * 4 + 1]), "r"(pk[q * 4 + 2]), "r"(pk[q * 4 + 3])
+                       : "memory");
+        }
+      }
+      l_run = l_run * alpha + rowsum;
+      m_run = m_new;
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full);
+      if (!mbar_wait_bounded(pv_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < HD / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + PV_COL + ch * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[ch * 32 + i] = o[ch * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+    }
+    const int t = qi * QT + r;
+    if (ok && t < p.T) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* op = p.out + (long long)(row0 + t) * p.C + h * HD;
+#pragma unroll
+      for (int q = 0; q < HD / 8; ++q) {
+        uint4 u;
+        u.x = pack_bf16x2(o[q * 8 + 0] * inv, o[q * 8 + 1] * inv);
+        u.y = pack_bf16x2(o[q * 8 + 2] * inv, o[q * 8 + 3] * inv);
+        u.z = pack_bf16x2(o[q * 8 + 4] * inv, o[q * 8 + 5] * inv);
+        u.w = pack_bf16x2(o[q * 8 + 6] * inv, o[q * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(op + q * 8) = u;
+      }
+      if (p.lse != nullptr)
+        p.lse[((long long)b * p.H + h) * p.T + t] = m_run * p.scale + __logf(l_run);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,
+              cudaStream_t stream) {
+  const int C = H * HD;
+  if (B <= 0 || T <= 0) return 0;
+  if (reinterpret_cast<uintptr_t>(qkv) & 15 || reinterpret_cast<uintptr_t>(out) & 15) return 1;
+  CUtensorMap tm;
+  if (!make_tma_2d_bf16(&tm, qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, HD, kSwizzle128)) return 2;
+  FwdParams p;
+  p.out = (__nv_bfloat16*)out;
+  p.lse = lse;
+  p.B = B; p.T = T; p.H = H; p.C = C;
+  p.scale = 0.125f;
+  p.scale_log2 = 0.125f * 1.4426950408889634f;
+  p.status = status;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    attr = true;
+  }
+  const int n_qt = (T + QT - 1) / QT;
+  flash_fwd_kernel<<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace z2h
+
+extern "C" int z2h_flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,
+                             void* stream) {
+  return z2h::flash_fwd(qkv, out, lse, B, T, H, status, (cudaStream_t)stream);
+}

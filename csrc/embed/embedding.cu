@@ -1,0 +1,131 @@
+// Token + position embedding for the GPT models.
+//
+// forward : out[m, :] = wte[idx[m], :] + wpe[m % T, :]                    (bf16)
+// backward: dwte[idx[m], :] += dx[m, :]   (fp32, vector red.global.add: rows of one token that
+//                                           occur in several positions are summed by the L2)
+//           dwpe[t, :]     += sum_b dx[b*T + t, :]  (fp32, one thread per column, fixed order)
+//
+// Out-of-range token ids are clamped into the table and counted in the status word instead
+// of faulting (the reference kernel bounds-checks ids as well, gpu-mojo/problems/p21/op/
+// embedding.mojo:13-60); the model-level semantics are nn/gpt2/modules.py:104-107.
+#include "../common/ptx.cuh"
+#include "embed.h"
+
+namespace z2h {
+namespace {
+
+template <typename IdxT>
+__global__ void embed_fwd_kernel(const IdxT* __restrict__ idx, const __nv_bfloat16* __restrict__ wte,
+                                 const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out,
+                                 int M, int T, int C, int V, int* status) {
+  const int vec_per_row = C / 8;
+  const long long total = (long long)M * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i / vec_per_row);
+    const int c = (int)(i % vec_per_row) * 8;
+    long long tok = (long long)idx[m];
+    if (tok < 0 || tok >= V) {
+      if (status != nullptr) atomicCAS(status, 0, (int)kBadArgument);
+      tok = tok < 0 ? 0 : V - 1;
+    }
+    const int t = m % T;
+    uint4 a = *reinterpret_cast<const uint4*>(wte + tok * C + c);
+    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z),
+           a3 = unpack_bf16x2(a.w);
+    if (wpe != nullptr) {
+      uint4 b = *reinterpret_cast<const uint4*>(wpe + (long long)t * C + c);
+      float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
+             b3 = unpack_bf16x2(b.w);
+      a0.x += b0.x; a0.y += b0.y; a1.x += b1.x; a1.y += b1.y;
+      a2.x += b2.x; a2.y += b2.y; a3.x += b3.x; a3.y += b3.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(a0.x, a0.y); o.y = pack_bf16x2(a1.x, a1.y);
+    o.z = pack_bf16x2(a2.x, a2.y); o.w = pack_bf16x2(a3.x, a3.y);
+    *reinterpret_cast<uint4*>(out + (long long)m * C + c) = o;
+  }
+}
+
+template <typename IdxT>
+__global__ void embed_bwd_wte_kernel(const IdxT* __restrict__ idx, const __nv_bfloat16* __restrict__ dx,
+                                     float* __restrict__ dwte, int M, int C, int V) {
+  const int vec_per_row = C / 4;
+  const long long total = (long long)M * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i / vec_per_row);
+    const int c = (int)(i % vec_per_row) * 4;
+    long long tok = (long long)idx[m];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+    uint2 a = *reinterpret_cast<const uint2*>(dx + (long long)m * C + c);
+    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y);
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dwte + tok * C + c),
+                 "f"(a0.x), "f"(a0.y), "f"(a1.x), "f"(a1.y)
+                 : "memory");
+  }
+}
+
+__global__ void embed_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dx, float* __restrict__ dwpe,
+                                     int B, int T, int C) {
+  const long long total = (long long)T * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int b = 0; b < B; ++b) s += __bfloat162float(dx[(long long)b * T * C + i]);
+    dwpe[i] += s;
+  }
+}
+
+}  // namespace
+
+int embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, void* out, int M,
+              int T, int C, int V, int* status, cudaStream_t stream) {
+  if (C % 8 != 0) return 1;
+  if (M <= 0) return 0;
+  const long long total = (long long)M * (C / 8);
+  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (idx_is_64)
+    embed_fwd_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)idx, (const __nv_bfloat16*)wte,
+                                                         (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out,
+                                                         M, T, C, V, status);
+  else
+    embed_fwd_kernel<int><<<grid, 256, 0, stream>>>((const int*)idx, (const __nv_bfloat16*)wte,
+                                                   (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out, M,
+                                                   T, C, V, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B, int T,
+              int C, int V, cudaStream_t stream) {
+  if (C % 8 != 0) return 1;
+  const int M = B * T;
+  if (M <= 0) return 0;
+  const long long total = (long long)M * (C / 4);
+  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (idx_is_64)
+    embed_bwd_wte_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)idx,
+                                                             (const __nv_bfloat16*)dx, dwte, M, C, V);
+  else
+    embed_bwd_wte_kernel<int><<<grid, 256, 0, stream>>>((const int*)idx, (const __nv_bfloat16*)dx,
+                                                       dwte, M, C, V);
+  if (dwpe != nullptr) {
+    const long long tc = (long long)T * C;
+    const int g2 = (int)((tc + 255) / 256 < 148 * 16 ? (tc + 255) / 256 : 148 * 16);
+    embed_bwd_wpe_kernel<<<g2, 256, 0, stream>>>((const __nv_bfloat16*)dx, dwpe, B, T, C);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace z2h
+
+extern "C" {
+int z2h_embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, void* out, int M,
+                  int T, int C, int V, int* status, void* stream) {
+  return z2h::embed_fwd(idx, idx_is_64, wte, wpe, out, M, T, C, V, status, (cudaStream_t)stream);
+}
+int z2h_embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B,
+                  int T, int C, int V, void* stream) {
+  return z2h::embed_bwd(idx, idx_is_64, dx, dwte, dwpe, B, T, C, V, (cudaStream_t)stream);
+}
+}

@@ -1,0 +1,133 @@
+"""Raw Python entry points of the sm_100a kernels (one function per C symbol).
+
+Every function takes torch CUDA tensors, launches on the current stream and returns
+immediately; nothing here allocates, so all of it can be captured into a CUDA graph. The
+autograd-aware, module-level API lives in `zero_to_hero_b200.ops.functional`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_float, c_void_p
+
+import torch
+
+from . import _lib
+from ._lib import ptr, stream_ptr
+
+_sigs = {
+    "z2h_layernorm_fwd": [c_void_p] * 6 + [c_int, c_int, c_float, c_void_p],
+    "z2h_layernorm_bwd_num_partials": [c_int],
+    "z2h_layernorm_bwd": [c_void_p] * 10 + [c_int, c_int, c_int, c_void_p],
+    "z2h_embed_fwd": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_void_p, c_void_p],
+    "z2h_embed_bwd": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "z2h_ce_fwd_bwd": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_longlong,
+                       c_float, c_int, c_int, c_void_p],
+    "z2h_reduce_sum": [c_void_p, c_int, c_float, c_void_p, c_int, c_void_p],
+    "z2h_gradnorm_partials": [c_void_p, c_longlong, c_void_p, c_void_p],
+    "z2h_adamw_step": [c_void_p] * 5 + [c_longlong, c_longlong, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_int, c_void_p],
+    "z2h_colsum_bf16": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p],
+    "z2h_cast_f32_to_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
+    "z2h_flash_fwd": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "z2h_flash_bwd": [c_void_p] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p],
+}
+_fns: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _f(name: str):
+    fn = _fns.get(name)
+    if fn is None:
+        fn = getattr(_lib.cuda_lib(), name)
+        fn.restype = c_int
+        fn.argtypes = _sigs[name]
+        _fns[name] = fn
+    return fn
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc} (1 bad argument, 2 tensor map, 3 launch)")
+
+
+def _is64(t: torch.Tensor) -> int:
+    assert t.dtype in (torch.int64, torch.int32)
+    return int(t.dtype == torch.int64)
+
+
+def layernorm_fwd(x, w, b, y, mean, rstd, eps=1e-5):
+    M, C = x.numel() // x.shape[-1], x.shape[-1]
+    _check(_f("z2h_layernorm_fwd")(ptr(x), ptr(w), ptr(b), ptr(y), ptr(mean), ptr(rstd), M, C,
+                                   eps, stream_ptr()), "layernorm_fwd")
+
+
+def layernorm_bwd_num_partials(M: int) -> int:
+    return _f("z2h_layernorm_bwd_num_partials")(M)
+
+
+def layernorm_bwd(dy, x, w, mean, rstd, dresid, dx, dw, db, scratch, accumulate=True):
+    M, C = x.numel() // x.shape[-1], x.shape[-1]
+    assert scratch.numel() >= layernorm_bwd_num_partials(M) * 2 * C
+    _check(_f("z2h_layernorm_bwd")(ptr(dy), ptr(x), ptr(w), ptr(mean), ptr(rstd), ptr(dresid),
+                                   ptr(dx), ptr(dw), ptr(db), ptr(scratch), M, C, int(accumulate),
+                                   stream_ptr()), "layernorm_bwd")
+
+
+def embed_fwd(idx, wte, wpe, out, T):
+    M, C = idx.numel(), wte.shape[1]
+    _check(_f("z2h_embed_fwd")(ptr(idx), _is64(idx), ptr(wte), ptr(wpe), ptr(out), M, T, C,
+                               wte.shape[0], ptr(_lib.status_word(out.device)), stream_ptr()),
+           "embed_fwd")
+
+
+def embed_bwd(idx, dx, dwte, dwpe, B, T):
+    C = dx.shape[-1]
+    _check(_f("z2h_embed_bwd")(ptr(idx), _is64(idx), ptr(dx), ptr(dwte), ptr(dwpe), B, T, C,
+                               dwte.shape[0], stream_ptr()), "embed_bwd")
+
+
+def ce_fwd_bwd(logits, targets, losses, v_real, grad_scale, write_grad=True, ignore_index=-100):
+    M, Vp = logits.shape
+    _check(_f("z2h_ce_fwd_bwd")(ptr(logits), ptr(targets), _is64(targets), ptr(losses), M, v_real,
+                                Vp, logits.stride(0), grad_scale, int(write_grad), ignore_index,
+                                stream_ptr()), "ce_fwd_bwd")
+
+
+def reduce_sum(x, out, scale=1.0, accumulate=False):
+    _check(_f("z2h_reduce_sum")(ptr(x), x.numel(), scale, ptr(out), int(accumulate), stream_ptr()),
+           "reduce_sum")
+
+
+def gradnorm_partials(g, partials) -> int:
+    n = _f("z2h_gradnorm_partials")(ptr(g), g.numel(), ptr(partials), stream_ptr())
+    if n < 0:
+        raise RuntimeError(f"gradnorm_partials failed with code {n}")
+    return n
+
+
+def adamw_step(p32, g, m, v, p16, n_decay, hyper, partials, num_partials, norm_out, zero_grad=True):
+    _check(_f("z2h_adamw_step")(ptr(p32), ptr(g), ptr(m), ptr(v), ptr(p16), p32.numel(), n_decay,
+                                ptr(hyper), ptr(partials), num_partials, ptr(norm_out),
+                                int(zero_grad), stream_ptr()), "adamw_step")
+
+
+def colsum_bf16(dy, db, accumulate=True):
+    M, N = dy.shape
+    _check(_f("z2h_colsum_bf16")(ptr(dy), M, N, dy.stride(0), ptr(db), int(accumulate),
+                                 stream_ptr()), "colsum_bf16")
+
+
+def cast_f32_to_bf16(src, dst):
+    _check(_f("z2h_cast_f32_to_bf16")(ptr(src), ptr(dst), src.numel(), stream_ptr()), "cast")
+
+
+def flash_fwd(qkv, out, lse, B, T, H):
+    _check(_f("z2h_flash_fwd")(ptr(qkv), ptr(out), ptr(lse), B, T, H,
+                               ptr(_lib.status_word(out.device)), stream_ptr()), "flash_fwd")
+
+
+def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, delta, B, T, H):
+    _check(_f("z2h_flash_bwd")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), ptr(dq_accum),
+                               ptr(delta), B, T, H, ptr(_lib.status_word(out.device)),
+                               stream_ptr()), "flash_bwd")
