@@ -1,0 +1,437 @@
+"""Fused GPT-2 training engine: one hand-scheduled forward/backward over flat buffers.
+
+Instead of an autograd graph (the reference trains through `loss.backward()` on a
+`torch.compile`d module, nn/gpt2/train.py:116-127, nn/gpt2/train_ddp.py:134-143) the engine
+owns
+
+* one flat fp32 master-parameter buffer, its bf16 working copy, one flat fp32 gradient buffer
+  and the AdamW moments; tensors with weight decay come first so a single index splits the
+  two AdamW groups (`dim() >= 2` rule of nn/gpt2/train.py:73-84);
+* every activation the backward pass needs, allocated once;
+* a fixed kernel schedule for a micro-step (embedding, per block LayerNorm -> QKV GEMM ->
+  flash attention -> projection GEMM with fused bias+residual -> LayerNorm -> GEMM with fused
+  bias+GELU -> GEMM with fused bias+residual, final LayerNorm, lm_head GEMM, fused
+  cross-entropy forward/backward, and the mirror-image backward with weight gradients
+  accumulated in fp32 straight into the flat gradient buffer), captured once in a CUDA graph
+  and replayed per micro-batch;
+* the optimizer step: global grad-norm, clipping, AdamW, bf16 re-cast and gradient zeroing in
+  two kernel launches, or, across ranks, the fused reduce-scatter + AdamW + all-gather kernel
+  of `zero_to_hero_b200.parallel.fused_ddp`.
+
+Gradient accumulation, absent from the reference, is the loop over micro-steps in
+`train_step`; the 1/(tokens * micro_steps * world) factor is folded into the cross-entropy
+backward so no separate scaling pass exists.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .config import Config, ModelConfig
+from .ops import _lib, gemm as G, native as N
+from .ops.functional import pick_split_k
+from .optim.schedule import lr_for
+
+ALIGN = 64  # elements; keeps every tensor 256-byte (fp32) / 128-byte (bf16) aligned
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple[int, ...]
+    offset: int
+    decay: bool
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+def _round_up(n: int, a: int = ALIGN) -> int:
+    return (n + a - 1) // a * a
+
+
+class ParamLayout:
+    """Flat-buffer layout of a GPT-2 model; names are the Hugging Face GPT-2 state_dict keys."""
+
+    def __init__(self, cfg: ModelConfig):
+        C, L, V, T = cfg.emb_dim, cfg.num_layers, cfg.vocab_size, cfg.block_size
+        decay: list[tuple[str, tuple[int, ...]]] = [
+            ("transformer.wte.weight", (V, C)),
+            ("transformer.wpe.weight", (T, C)),
+        ]
+        no_decay: list[tuple[str, tuple[int, ...]]] = []
+        for i in range(L):
+            p = f"transformer.h.{i}."
+            decay += [
+                (p + "attn.c_attn.weight", (3 * C, C)),
+                (p + "attn.c_proj.weight", (C, C)),
+                (p + "mlp.c_fc.weight", (4 * C, C)),
+                (p + "mlp.c_proj.weight", (C, 4 * C)),
+            ]
+            no_decay += [(p + "ln_1.weight", (C,))]
+            if cfg.ln_bias:
+                no_decay += [(p + "ln_1.bias", (C,))]
+            no_decay += [(p + "attn.c_attn.bias", (3 * C,)), (p + "attn.c_proj.bias", (C,)),
+                         (p + "ln_2.weight", (C,))]
+            if cfg.ln_bias:
+                no_decay += [(p + "ln_2.bias", (C,))]
+            no_decay += [(p + "mlp.c_fc.bias", (4 * C,)), (p + "mlp.c_proj.bias", (C,))]
+        no_decay += [("transformer.ln_f.weight", (C,))]
+        if cfg.ln_bias:
+            no_decay += [("transformer.ln_f.bias", (C,))]
+        self.specs: dict[str, ParamSpec] = {}
+        off = 0
+        for name, shape in decay:
+            self.specs[name] = ParamSpec(name, shape, off, True)
+            off = _round_up(off + math.prod(shape))
+        self.n_decay = off
+        for name, shape in no_decay:
+            self.specs[name] = ParamSpec(name, shape, off, False)
+            off = _round_up(off + math.prod(shape))
+        self.total = off
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        s = self.specs[name]
+        return flat[s.offset:s.offset + s.numel].view(s.shape)
+
+    def num_params(self) -> int:
+        return sum(s.numel for s in self.specs.values())
+
+
+class GPT2TrainEngine:
+    """Trains a GPT-2 (`ModelConfig.kind == "gpt2"`) on one GPU, or one rank of a DDP job."""
+
+    def __init__(self, cfg: Config, device: torch.device | str = "cuda", comm=None,
+                 seed: int | None = None):
+        mc = cfg.model
+        if mc.kind != "gpt2":
+            raise ValueError("the fused engine implements the GPT-2 architecture")
+        if mc.head_dim != 64:
+            raise ValueError("the flash-attention kernels are written for head_dim 64")
+        if mc.dropout != 0.0:
+            raise ValueError("the fused engine runs without dropout; use the module path for dropout")
+        if mc.emb_dim % 8 or mc.emb_dim > 2048:
+            raise ValueError("emb_dim must be a multiple of 8 and at most 2048")
+        self.cfg = cfg
+        self.mc = mc
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise ValueError("GPT2TrainEngine needs a CUDA device (use models.GPT2 on CPU)")
+        _lib.cuda_lib()  # fail loudly here if the native library was not built
+        self.comm = comm
+        self.world = 1 if comm is None else comm.world_size
+        self.rank = 0 if comm is None else comm.rank
+        self.layout = ParamLayout(mc)
+        P = self.layout.total
+        dev = self.device
+        f32, bf16 = torch.float32, torch.bfloat16
+        if comm is None:
+            self.p16 = torch.zeros(P, device=dev, dtype=bf16)
+            self.g = torch.zeros(P, device=dev, dtype=f32)
+            self.p32 = torch.zeros(P, device=dev, dtype=f32)
+            self.m = torch.zeros(P, device=dev, dtype=f32)
+            self.v = torch.zeros(P, device=dev, dtype=f32)
+        else:
+            # gradients and the bf16 working copy live in peer-visible memory; the fp32 master
+            # copy and the moments exist only for the shard this rank owns
+            comm.setup(P, self.layout.n_decay)
+            self.p16, self.g = comm.p16, comm.g
+            self.p32, self.m, self.v = comm.p32_shard, comm.m_shard, comm.v_shard
+        self.hyper = torch.zeros(16, device=dev, dtype=f32)
+        self.hyper_host = torch.zeros(16, dtype=f32).pin_memory()
+        self.partials = torch.zeros(1024, device=dev, dtype=f32)
+        self.norm = torch.zeros(1, device=dev, dtype=f32)
+        self.loss_accum = torch.zeros(1, device=dev, dtype=f32)
+        self.loss_host = torch.zeros(1, dtype=f32).pin_memory()
+        self.opt_step = 0
+        self._alloc_activations(cfg.train.micro_batch, mc.block_size)
+        self._graph = None
+        self._graph_scale = None
+        self.launches_per_micro_step = 0
+        self.init_weights(cfg.train.seed if seed is None else seed)
+
+    # ------------------------------------------------------------------ parameters
+    def init_weights(self, seed: int) -> None:
+        """N(0, 0.02) for matrices and embeddings, residual projections scaled by
+        1/sqrt(2 L), biases 0, LayerNorm weights 1 (nn/gpt2/modules.py:87-100)."""
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        full = torch.zeros(self.layout.total, dtype=torch.float32)
+        L = self.mc.num_layers
+        for name, s in self.layout.specs.items():
+            v = full[s.offset:s.offset + s.numel].view(s.shape)
+            if name.endswith("ln_1.weight") or name.endswith("ln_2.weight") or name.endswith("ln_f.weight"):
+                v.fill_(1.0)
+            elif name.endswith(".bias"):
+                v.zero_()
+            else:
+                std = 0.02 / math.sqrt(2 * L) if name.endswith("c_proj.weight") else 0.02
+                v.normal_(0.0, std, generator=gen)
+        self.load_flat(full)
+
+    def load_flat(self, full_fp32: torch.Tensor) -> None:
+        """Install a full flat fp32 parameter vector (every rank passes the same values)."""
+        full = full_fp32.to(self.device, torch.float32)
+        self.p16.copy_(full.bfloat16())
+        if self.comm is None:
+            self.p32.copy_(full)
+        else:
+            self.comm.load_master(full)
+        self.m.zero_()
+        self.v.zero_()
+        self.g.zero_()
+        self.opt_step = 0
+
+    def full_master(self) -> torch.Tensor:
+        """The complete fp32 master vector (gathered across ranks when sharded)."""
+        if self.comm is None:
+            return self.p32.clone()
+        return self.comm.gather_master()
+
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        """fp32 parameters under Hugging Face GPT-2 names (Linear weights as (out, in))."""
+        full = self.full_master()
+        sd = {n: self.layout.view(full, n).clone() for n in self.layout.specs}
+        sd["lm_head.weight"] = sd["transformer.wte.weight"]
+        return sd
+
+    def load_state_dict(self, sd: dict[str, torch.Tensor]) -> None:
+        full = torch.zeros(self.layout.total, dtype=torch.float32)
+        for n, s in self.layout.specs.items():
+            full[s.offset:s.offset + s.numel] = sd[n].detach().float().reshape(-1).cpu()
+        self.load_flat(full)
+
+    def load_from_module(self, model: torch.nn.Module) -> None:
+        self.load_state_dict(model.state_dict())
+
+    def w(self, name: str) -> torch.Tensor:
+        return self.layout.view(self.p16, name)
+
+    def gw(self, name: str) -> torch.Tensor:
+        return self.layout.view(self.g, name)
+
+    # ------------------------------------------------------------------ activations
+    def _alloc_activations(self, B: int, T: int) -> None:
+        mc, dev = self.mc, self.device
+        C, L, H = mc.emb_dim, mc.num_layers, mc.num_heads
+        M = B * T
+        self.B, self.T, self.M = B, T, M
+        bf16, f32 = torch.bfloat16, torch.float32
+
+        def buf(*shape, dtype=bf16):
+            return torch.empty(*shape, device=dev, dtype=dtype)
+
+        self.idx = torch.zeros(B, T, device=dev, dtype=torch.int64)
+        self.tgt = torch.zeros(B, T, device=dev, dtype=torch.int64)
+        self.resid = [buf(M, C) for _ in range(L + 1)]
+        self.x_mid = [buf(M, C) for _ in range(L)]
+        self.xn1 = [buf(M, C) for _ in range(L)]
+        self.xn2 = [buf(M, C) for _ in range(L)]
+        self.stats = [[buf(M, dtype=f32) for _ in range(4)] for _ in range(L)]
+        self.qkv = [buf(M, 3 * C) for _ in range(L)]
+        self.att = [buf(M, C) for _ in range(L)]
+        self.lse = [buf(B, H, T, dtype=f32) for _ in range(L)]
+        self.pre = [buf(M, 4 * C) for _ in range(L)]
+        self.act = [buf(M, 4 * C) for _ in range(L)]
+        self.xf = buf(M, C)
+        self.stats_f = [buf(M, dtype=f32) for _ in range(2)]
+        self.Vp = mc.padded_vocab
+        self.logits = torch.zeros(M, self.Vp, device=dev, dtype=bf16)
+        self.losses = buf(M, dtype=f32)
+        # backward scratch
+        self.d_resid = buf(M, C)
+        self.d_c = buf(M, C)
+        self.d_4c = buf(M, 4 * C)
+        self.d_qkv = buf(M, 3 * C)
+        self.dq_accum = buf(M, C, dtype=f32)
+        self.delta = buf(B, H, T, dtype=f32)
+        self.ln_scratch = buf(N.layernorm_bwd_num_partials(M) * 2 * C, dtype=f32)
+
+    # ------------------------------------------------------------------ kernels schedule
+    def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, name: str) -> None:
+        """g[name] += dy^T x with fp32 accumulation straight into the flat gradient buffer."""
+        out = self.gw(name)
+        n_out, k_in = out.shape
+        tiles = math.ceil(n_out / 128) * math.ceil(k_in / 256)
+        sk = pick_split_k(tiles, math.ceil(dy.shape[0] / 64))
+        if sk == 1:
+            G.gemm(dy, x, out, a_mn=True, b_mn=True, epi=G.EPI_ACCUMULATE)
+        else:
+            G.gemm(dy, x, out, a_mn=True, b_mn=True, epi=G.EPI_ATOMIC_ADD, split_k=sk)
+        self._n += 1
+
+    def _forward_backward(self, grad_scale: float, loss_scale: float) -> None:
+        """One micro-step on the static buffers `idx` / `tgt` (all launches, no host sync)."""
+        mc = self.mc
+        C, L, H, V = mc.emb_dim, mc.num_layers, mc.num_heads, mc.vocab_size
+        B, T, M = self.B, self.T, self.M
+        w, gw = self.w, self.gw
+        has_lnb = mc.ln_bias
+        self._n = 0
+
+        def lnb(name):
+            return w(name) if has_lnb else None
+
+        def glnb(name):
+            return gw(name) if has_lnb else None
+
+        # ---------------- forward
+        N.embed_fwd(self.idx, w("transformer.wte.weight"), w("transformer.wpe.weight"),
+                    self.resid[0], T)
+        self._n += 1
+        for l in range(L):
+            p = f"transformer.h.{l}."
+            st = self.stats[l]
+            N.layernorm_fwd(self.resid[l], w(p + "ln_1.weight"), lnb(p + "ln_1.bias"), self.xn1[l],
+                            st[0], st[1])
+            G.gemm(self.xn1[l], w(p + "attn.c_attn.weight"), self.qkv[l], bias=w(p + "attn.c_attn.bias"))
+            N.flash_fwd(self.qkv[l], self.att[l], self.lse[l], B, T, H)
+            G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.x_mid[l],
+                   bias=w(p + "attn.c_proj.bias"), residual=self.resid[l], epi=G.EPI_RESIDUAL)
+            N.layernorm_fwd(self.x_mid[l], w(p + "ln_2.weight"), lnb(p + "ln_2.bias"), self.xn2[l],
+                            st[2], st[3])
+            G.gemm(self.xn2[l], w(p + "mlp.c_fc.weight"), self.act[l], bias=w(p + "mlp.c_fc.bias"),
+                   aux_out=self.pre[l], epi=G.EPI_GELU)
+            G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.resid[l + 1],
+                   bias=w(p + "mlp.c_proj.bias"), residual=self.x_mid[l], epi=G.EPI_RESIDUAL)
+            self._n += 7
+        N.layernorm_fwd(self.resid[L], w("transformer.ln_f.weight"), lnb("transformer.ln_f.bias"),
+                        self.xf, self.stats_f[0], self.stats_f[1])
+        logits_v = self.logits[:, :V]
+        G.gemm(self.xf, w("transformer.wte.weight"), logits_v)
+        # loss and d(logits) in one pass, in place
+        N.ce_fwd_bwd(self.logits, self.tgt, self.losses, V, grad_scale)
+        N.reduce_sum(self.losses, self.loss_accum, scale=loss_scale, accumulate=True)
+        self._n += 4
+
+        # ---------------- backward
+        G.gemm(logits_v, w("transformer.wte.weight"), self.d_c, b_mn=True)
+        self._n += 1
+        self._wgrad(logits_v, self.xf, "transformer.wte.weight")
+        N.layernorm_bwd(self.d_c, self.resid[L], w("transformer.ln_f.weight"), self.stats_f[0],
+                        self.stats_f[1], None, self.d_resid, gw("transformer.ln_f.weight"),
+                        glnb("transformer.ln_f.bias"), self.ln_scratch)
+        self._n += 2
+        for l in reversed(range(L)):
+            p = f"transformer.h.{l}."
+            st = self.stats[l]
+            # MLP
+            self._wgrad(self.d_resid, self.act[l], p + "mlp.c_proj.weight")
+            N.colsum_bf16(self.d_resid, gw(p + "mlp.c_proj.bias"))
+            G.gemm(self.d_resid, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
+                   aux_in=self.pre[l], epi=G.EPI_GELU_GRAD)
+            self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
+            N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
+            G.gemm(self.d_4c, w(p + "mlp.c_fc.weight"), self.d_c, b_mn=True)
+            N.layernorm_bwd(self.d_c, self.x_mid[l], w(p + "ln_2.weight"), st[2], st[3],
+                            self.d_resid, self.d_resid, gw(p + "ln_2.weight"), glnb(p + "ln_2.bias"),
+                            self.ln_scratch)
+            # attention
+            self._wgrad(self.d_resid, self.att[l], p + "attn.c_proj.weight")
+            N.colsum_bf16(self.d_resid, gw(p + "attn.c_proj.bias"))
+            G.gemm(self.d_resid, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
+            N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
+                        self.delta, B, T, H)
+            self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
+            N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
+            G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)
+            N.layernorm_bwd(self.d_c, self.resid[l], w(p + "ln_1.weight"), st[0], st[1],
+                            self.d_resid, self.d_resid, gw(p + "ln_1.weight"), glnb(p + "ln_1.bias"),
+                            self.ln_scratch)
+            self._n += 4 + 4 + 2 * 2 + 3  # dgrad GEMMs, column sums, LN bwd (2 kernels each), flash bwd (3)
+        N.embed_bwd(self.idx, self.d_resid, gw("transformer.wte.weight"),
+                    gw("transformer.wpe.weight"), B, T)
+        self._n += 2
+        self.launches_per_micro_step = self._n
+
+    # ------------------------------------------------------------------ public stepping API
+    def micro_steps_per_step(self) -> int:
+        tokens = self.B * self.T * self.world
+        n = max(1, self.cfg.train.total_batch_tokens // tokens)
+        return n
+
+    def micro_step(self, idx: torch.Tensor, tgt: torch.Tensor, accum_steps: int) -> None:
+        """Forward + backward on one micro-batch; `idx`/`tgt` may be pinned host or device
+        tensors of shape [micro_batch, block_size]. Gradients accumulate in the flat buffer."""
+        self.idx.copy_(idx, non_blocking=True)
+        self.tgt.copy_(tgt, non_blocking=True)
+        grad_scale = 1.0 / (self.M * accum_steps * self.world)
+        loss_scale = 1.0 / (self.M * accum_steps)
+        if not self.cfg.train.use_cuda_graph:
+            self._forward_backward(grad_scale, loss_scale)
+            return
+        if self._graph is None or self._graph_scale != (grad_scale, loss_scale):
+            # warm-up outside capture (sets function attributes, loads modules), then undo its
+            # side effects on the gradient / loss accumulators by capturing from a clean slate
+            g_backup = self.g.clone()
+            loss_backup = self.loss_accum.clone()
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._forward_backward(grad_scale, loss_scale)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            _lib.check_status(self.device)
+            self.g.copy_(g_backup)
+            self.loss_accum.copy_(loss_backup)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._forward_backward(grad_scale, loss_scale)
+            self.g.copy_(g_backup)
+            self.loss_accum.copy_(loss_backup)
+            del g_backup
+            self._graph, self._graph_scale = graph, (grad_scale, loss_scale)
+        self._graph.replay()
+
+    def _write_hyper(self, lr: float) -> None:
+        oc = self.cfg.optim
+        t = self.opt_step
+        h = self.hyper_host
+        h[0], h[1], h[2], h[3], h[4] = lr, oc.beta1, oc.beta2, oc.eps, oc.weight_decay
+        h[5], h[6] = 1.0 - oc.beta1 ** t, 1.0 - oc.beta2 ** t
+        h[7], h[8] = oc.clip_norm, 1.0
+        self.hyper.copy_(h, non_blocking=True)
+
+    def optimizer_step(self, lr: float | None = None) -> None:
+        """Global grad-norm clip + AdamW + bf16 re-cast + gradient zeroing."""
+        self.opt_step += 1
+        if lr is None:
+            lr = lr_for(self.opt_step - 1, self.cfg.optim)
+        self._write_hyper(lr)
+        if self.comm is None:
+            n = N.gradnorm_partials(self.g, self.partials)
+            N.adamw_step(self.p32, self.g, self.m, self.v, self.p16, self.layout.n_decay, self.hyper,
+                         self.partials, n, self.norm, zero_grad=True)
+        else:
+            self.comm.fused_step(self.hyper, self.norm)
+
+    def train_step(self, batches, lr: float | None = None) -> None:
+        """One optimizer step over an iterable of (idx, tgt) micro-batches. Asynchronous: read
+        the result with `read_loss()`."""
+        batches = list(batches)
+        self.loss_accum.zero_()
+        for idx, tgt in batches:
+            self.micro_step(idx, tgt, len(batches))
+        self.optimizer_step(lr)
+
+    def read_loss(self) -> float:
+        """Device -> host read of the mean loss of the last step (synchronises the stream)."""
+        self.loss_host.copy_(self.loss_accum, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self.loss_host[0])
+
+    def read_grad_norm(self) -> float:
+        return float(self.norm.item())
+
+    # ------------------------------------------------------------------ inference helpers
+    @torch.no_grad()
+    def export_to_module(self, model: torch.nn.Module) -> None:
+        sd = self.state_dict()
+        model.load_state_dict({k: v for k, v in sd.items()}, strict=False)
+
+    def kernel_launches_per_step(self, micro_steps: int) -> int:
+        """How many of this library's kernels one optimizer step launches."""
+        opt = 2 if self.comm is None else self.comm.launches_per_step
+        return self.launches_per_micro_step * micro_steps + opt
