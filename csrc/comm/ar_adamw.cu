@@ -377,6 +377,14 @@ allreduce_ag_kernel(Peers bufs, Peers pads, int rank, int world, long long shard
   }
 }
 
+// Waits on one slot of a pad for a given epoch; used to exercise the bounded wait on one GPU.
+__global__ void wait_probe_kernel(uint64_t* pad, int kind, int src, uint32_t epoch,
+                                  uint64_t budget_ns, int* status, int* result) {
+  uint64_t v = 0;
+  const bool ok = wait_slot(slot(pad, kind, src), epoch, budget_ns, &v, status);
+  *result = ok ? 1 : 0;
+}
+
 Peers to_peers(void* const* p, int world) {
   Peers t;
   for (int i = 0; i < kMaxRanks; ++i) t.ptr[i] = i < world ? p[i] : nullptr;
@@ -447,9 +455,21 @@ int allreduce(void* const* bufs, void* const* pads, void* out, int rank, int wor
                                        budget_ns, status, max_ctas, stream);
 }
 
+int wait_probe(void* pad, int kind, int src, uint32_t epoch, uint64_t budget_ns, int* status,
+               int* result, cudaStream_t stream) {
+  if (kind < 0 || kind >= 8 || src < 0 || src >= kMaxRanks) return 1;
+  wait_probe_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<uint64_t*>(pad), kind, src, epoch, budget_ns,
+                                         status, result);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
 }  // namespace z2h
 
 extern "C" {
+int z2h_wait_probe(void* pad, int kind, int src, unsigned int epoch, unsigned long long budget_ns,
+                   int* status, int* result, void* stream) {
+  return z2h::wait_probe(pad, kind, src, epoch, budget_ns, status, result, (cudaStream_t)stream);
+}
 int z2h_fused_step_twoshot(void* const* grads, void* const* p16, void* const* pads, float* p32,
                            float* m, float* v, int rank, int world, long long shard_off,
                            long long shard_n, long long total_n, long long n_decay,

@@ -42,4 +42,9 @@ int allreduce(void* const* bufs, void* const* pads, void* out, int rank, int wor
               int dtype, int algo, uint32_t* epoch, unsigned int* done_counter, uint64_t budget_ns,
               int* status, int max_ctas, cudaStream_t stream);
 
+// Single-thread kernel that waits (bounded) for pad slot (kind, src) to reach `epoch`; writes 1 to
+// *result on success, 0 after the budget ran out (and kTimeoutPeer to *status).
+int wait_probe(void* pad, int kind, int src, uint32_t epoch, uint64_t budget_ns, int* status,
+               int* result, cudaStream_t stream);
+
 }  // namespace z2h

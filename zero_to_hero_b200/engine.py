@@ -435,3 +435,36 @@ class GPT2TrainEngine:
         """How many of this library's kernels one optimizer step launches."""
         opt = 2 if self.comm is None else self.comm.launches_per_step
         return self.launches_per_micro_step * micro_steps + opt
+
+
+def save_engine_checkpoint(engine: GPT2TrainEngine, path, data_state=None) -> None:
+    """Rank 0 writes model (GPT-2 names), flat AdamW moments, step, RNG, data cursor, config."""
+    from .utils.checkpoint import save_checkpoint
+
+    if engine.comm is None:
+        m, v = engine.m.cpu(), engine.v.cpu()
+    else:
+        m, v = engine.comm.gather_shards(engine.m).cpu(), engine.comm.gather_shards(engine.v).cpu()
+    sd = engine.state_dict()  # gathers the sharded master weights: every rank takes part
+    if engine.rank == 0:
+        save_checkpoint(path, sd, {"kind": "flat-adamw", "m": m, "v": v,
+                                                    "opt_step": engine.opt_step},
+                        engine.opt_step, data_state, engine.cfg.to_dict())
+
+
+def load_engine_checkpoint(engine: GPT2TrainEngine, path) -> dict:
+    from .utils.checkpoint import load_checkpoint, set_rng_state
+
+    ck = load_checkpoint(path)
+    engine.load_state_dict(ck["model"])
+    opt = ck["optim"]
+    if opt and opt.get("kind") == "flat-adamw":
+        if engine.comm is None:
+            engine.m.copy_(opt["m"])
+            engine.v.copy_(opt["v"])
+        else:
+            engine.comm.scatter_shards(opt["m"], engine.m)
+            engine.comm.scatter_shards(opt["v"], engine.v)
+        engine.opt_step = int(opt["opt_step"])
+    set_rng_state(ck["rng"])
+    return ck
