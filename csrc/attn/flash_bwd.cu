@@ -22,6 +22,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
+#include <cstdlib>
 
 namespace z2h {
 namespace {
@@ -31,20 +32,22 @@ constexpr int HD = 64;
 constexpr int TILE_BYTES = TS * HD * 2;  // 16 KiB
 constexpr int PT_BYTES = TS * TS * 2;    // 32 KiB
 constexpr int Q_STAGES = 2;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps
+constexpr int NUM_COMPUTE = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384;
 constexpr int SMEM_BYTES =
     1024 + 2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + 2 * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
 
 struct BwdParams {
-  const float* lse;
-  const float* delta;
+  const float* stats;  // [2][B*H][Tpad]: lse * log2(e), then delta; zero beyond T
+  int Tpad;
   __nv_bfloat16* dqkv;
   float* dq_accum;
   int B, T, H, C;
   float scale, scale_log2;
   int* status;
+  int debug;
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -68,8 +71,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   uint64_t* st_full = qdo_empty + Q_STAGES;
   uint64_t* pds_full = st_full + 1;
   uint64_t* dq_full = pds_full + 1;
-  uint64_t* stat_full = dq_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,9 +90,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(st_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, NUM_COMPUTE / 32);
     mbar_init(dq_full, 1);
-    mbar_init(stat_full, 128);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -115,9 +116,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         const int s = it % Q_STAGES;
         const uint32_t ph = (it / Q_STAGES) & 1;
         if (!mbar_wait_bounded(&qdo_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
-        mbar_arrive_expect_tx(&qdo_full[s], 2 * TILE_BYTES);
+        mbar_arrive_expect_tx(&qdo_full[s], 2 * TILE_BYTES + 2 * TS * 4);
         tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &qdo_full[s], h * HD, row0 + i * TS);
         tma_load_2d(sdO + s * TILE_BYTES, &tm_do, &qdo_full[s], h * HD, row0 + i * TS);
+        const float* st_row = p.stats + (long long)bh * p.Tpad + i * TS;
+        bulk_load_1d(sLse + s * TS, st_row, TS * 4, &qdo_full[s]);
+        bulk_load_1d(sDelta + s * TS, st_row + (long long)p.B * p.H * p.Tpad, TS * 4, &qdo_full[s]);
       }
       if (*abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -130,19 +134,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       constexpr uint32_t idesc_st = make_idesc_bf16(TS, TS, 0, 0);
       constexpr uint32_t idesc_dvk = make_idesc_bf16(TS, HD, 0, 1);
       constexpr uint32_t idesc_dq = make_idesc_bf16(TS, HD, 1, 1);
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      const uint32_t pt_addr = smem_u32(sPt), dst_addr = smem_u32(sdSt);
+      // descriptors are built once; inside the loop an MMA costs one 64-bit add per operand
+      const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t pt_desc = make_smem_desc_sw128(smem_u32(sPt), 16, 1024);
+      const uint64_t dst_desc = make_smem_desc_sw128(smem_u32(sdSt), 16, 1024);
+      const uint64_t dst_mn_desc = make_smem_desc_sw128(smem_u32(sdSt), TS * 128, 1024);
+      uint64_t q_desc[Q_STAGES], do_desc[Q_STAGES];
+#pragma unroll
+      for (int s = 0; s < Q_STAGES; ++s) {
+        q_desc[s] = make_smem_desc_sw128(smem_u32(sQ + s * TILE_BYTES), 16, 1024);
+        do_desc[s] = make_smem_desc_sw128(smem_u32(sdO + s * TILE_BYTES), 16, 1024);
+      }
       auto issue_st = [&](int s) {
-        const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES);
-        const uint32_t do_addr = smem_u32(sdO + s * TILE_BYTES);
+        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
+        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          tc_mma_f16_ss(tmem_base + ST_COL, make_smem_desc_sw128(k_addr + k * 32, 16, 1024),
-                        make_smem_desc_sw128(q_addr + k * 32, 16, 1024), idesc_st, k > 0);
+          tc_mma_f16_ss(tmem_base + ST_COL, desc_advance(k_desc, k * 32), desc_advance(qd, k * 32),
+                        idesc_st, k > 0);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          tc_mma_f16_ss(tmem_base + DPT_COL, make_smem_desc_sw128(v_addr + k * 32, 16, 1024),
-                        make_smem_desc_sw128(do_addr + k * 32, 16, 1024), idesc_st, k > 0);
+          tc_mma_f16_ss(tmem_base + DPT_COL, desc_advance(v_desc, k * 32), desc_advance(dod, k * 32),
+                        idesc_st, k > 0);
         tc_commit(st_full);
       };
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFull);
@@ -155,27 +169,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         const int s = it % Q_STAGES;
         if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES);
-        const uint32_t do_addr = smem_u32(sdO + s * TILE_BYTES);
+        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
+        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
           const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + DV_COL, make_smem_desc_sw128(pt_addr + a_off, 16, 1024),
-                        make_smem_desc_sw128(do_addr + k * 2048, 16, 1024), idesc_dvk,
-                        (it > 0 || k > 0) ? 1u : 0u);
+          tc_mma_f16_ss(tmem_base + DV_COL, desc_advance(pt_desc, a_off), desc_advance(dod, k * 2048),
+                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
           const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + DK_COL, make_smem_desc_sw128(dst_addr + a_off, 16, 1024),
-                        make_smem_desc_sw128(q_addr + k * 2048, 16, 1024), idesc_dvk,
-                        (it > 0 || k > 0) ? 1u : 0u);
+          tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
+                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
-          tc_mma_f16_ss(tmem_base + DQ_COL,
-                        make_smem_desc_sw128(dst_addr + k * 2048, TS * 128, 1024),
-                        make_smem_desc_sw128(k_addr + k * 2048, 16, 1024), idesc_dq, k > 0);
+          tc_mma_f16_ss(tmem_base + DQ_COL, desc_advance(dst_mn_desc, k * 2048),
+                        desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
         }
         tc_commit(dq_full);
         tc_commit(&qdo_empty[s]);
@@ -189,25 +200,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       }
     }
   } else {
+    // Two warps share each TMEM lane quarter: warp (2 + q) takes query columns 0..63 of a key
+    // row, warp (6 + q) columns 64..127, so every SM sub-partition has two compute warps.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;  // key row (S^T, dV, dK) or query row (dQ) == TMEM lane
-    const int ct = threadIdx.x - 64;    // 0..127 among the compute threads
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
-    const uint32_t pt_row = smem_u32(sPt) + r * 128;
-    const uint32_t dst_row = smem_u32(sdSt) + r * 128;
-    const long long stat_base = ((long long)b * p.H + h) * p.T;
+    const uint32_t pt_row = smem_u32(sPt) + half * (TS * 128) + r * 128;
+    const uint32_t dst_row = smem_u32(sdSt) + half * (TS * 128) + r * 128;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int i = j + it;
       const int s = it % Q_STAGES;
-      // stage the per-query statistics of this q tile (one value per compute thread)
-      {
-        const int t = i * TS + ct;
-        sLse[s * TS + ct] = t < p.T ? p.lse[stat_base + t] * 1.4426950408889634f : 0.f;
-        sDelta[s * TS + ct] = t < p.T ? p.delta[stat_base + t] : 0.f;
-      }
-      mbar_arrive(stat_full);
-      if (!mbar_wait_bounded(stat_full, it & 1, abort_flag, p.status, kTimeoutLocal)) {
+      // the per-query statistics of this q tile arrive with the Q / dO tiles (bulk copies)
+      if (!mbar_wait_bounded(&qdo_full[s], (it / Q_STAGES) & 1, abort_flag, p.status, kTimeoutFull)) {
         ok = false;
         break;
       }
@@ -218,59 +224,76 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tc_fence_after();
       const bool diag = (i == j);
       const int q_valid = p.T - i * TS;  // columns >= q_valid are past the end of the sequence
-      const float* lse2 = sLse + s * TS;
-      const float* dlt = sDelta + s * TS;
-#pragma unroll 1
-      for (int ch = 0; ch < TS / 32; ++ch) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(t_lane + ST_COL + ch * 32, sv);
-        tmem_ld_32x32b_x32(t_lane + DPT_COL + ch * 32, dv);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+      const bool fast = !diag && q_valid >= TS;  // no masking anywhere in this tile
+      const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * TS + half * 64);
+      const float4* dlt4 = reinterpret_cast<const float4*>(sDelta + s * TS + half * 64);
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64, sv[0]);
+      tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64, dv[0]);
+      tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64 + 32, sv[1]);
+      tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64 + 32, dv[1]);
+      tmem_ld_wait();
+      if (!(p.debug & 4))
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const int c0 = ch * 32 + e, c1 = c0 + 1;
-          float p0 = exp2f(__uint_as_float(sv[e]) * p.scale_log2 - lse2[c0]);
-          float p1 = exp2f(__uint_as_float(sv[e + 1]) * p.scale_log2 - lse2[c1]);
-          if ((diag && c0 < r) || c0 >= q_valid) p0 = 0.f;
-          if ((diag && c1 < r) || c1 >= q_valid) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dv[e]) - dlt[c0]);
-          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dlt[c1]);
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-          dk[e >> 1] = pack_bf16x2(d0, d1);
-        }
-        const uint32_t atom_off = (ch >> 1) * (TS * 128);
+      for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint32_t chunk = ((uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7)) * 16;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + atom_off + chunk),
-                       "r"(pk[q * 4 + 0]), "r"(pk[q * 4 + 1]), "r"(pk[q * 4 + 2]), "r"(pk[q * 4 + 3])
+          uint32_t pk[4], dk[4];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int e4 = q * 2 + e;
+            const float4 L = lse4[ch * 8 + e4];
+            const float4 D = dlt4[ch * 8 + e4];
+            float p0 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 0]), p.scale_log2, -L.x));
+            float p1 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 1]), p.scale_log2, -L.y));
+            float p2 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 2]), p.scale_log2, -L.z));
+            float p3 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 3]), p.scale_log2, -L.w));
+            if (!fast) {
+              const int c0 = half * 64 + ch * 32 + e4 * 4;
+              if ((diag && c0 + 0 < r) || c0 + 0 >= q_valid) p0 = 0.f;
+              if ((diag && c0 + 1 < r) || c0 + 1 >= q_valid) p1 = 0.f;
+              if ((diag && c0 + 2 < r) || c0 + 2 >= q_valid) p2 = 0.f;
+              if ((diag && c0 + 3 < r) || c0 + 3 >= q_valid) p3 = 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(dv[ch][e4 * 4 + 0]) - D.x);
+            const float d1 = p1 * (__uint_as_float(dv[ch][e4 * 4 + 1]) - D.y);
+            const float d2 = p2 * (__uint_as_float(dv[ch][e4 * 4 + 2]) - D.z);
+            const float d3 = p3 * (__uint_as_float(dv[ch][e4 * 4 + 3]) - D.w);
+            pk[e * 2 + 0] = pack_bf16x2(p0, p1);
+            pk[e * 2 + 1] = pack_bf16x2(p2, p3);
+            dk[e * 2 + 0] = pack_bf16x2(d0, d1);
+            dk[e * 2 + 1] = pack_bf16x2(d2, d3);
+          }
+          // 8 columns = one 16-byte chunk of this row inside swizzle atom `half`
+          const uint32_t chunk = ((uint32_t)(ch * 4 + q) ^ (uint32_t)(r & 7)) * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + chunk), "r"(pk[0]),
+                       "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                        : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + atom_off + chunk),
-                       "r"(dk[q * 4 + 0]), "r"(dk[q * 4 + 1]), "r"(dk[q * 4 + 2]), "r"(dk[q * 4 + 3])
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + chunk), "r"(dk[0]),
+                       "r"(dk[1]), "r"(dk[2]), "r"(dk[3])
                        : "memory");
         }
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);  // one arrival per compute warp
       if (!mbar_wait_bounded(dq_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      // dQ tile: TMEM lane == query row of tile i
+      // dQ tile: TMEM lane == query row of tile i; this warp takes 32 of the 64 columns
       const int tq = i * TS + r;
-      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD;
-#pragma unroll
-      for (int ch = 0; ch < HD / 32; ++ch) {
+      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD + half * 32;
+      {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + DQ_COL + ch * 32, v);
+        tmem_ld_32x32b_x32(t_lane + DQ_COL + half * 32, v);
         tmem_ld_wait();
-        if (tq < p.T) {
+        if (tq < p.T && !(p.debug & 1)) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + ch * 32 + q * 4),
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 4),
                          "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
                          "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
                          : "memory");
@@ -282,36 +305,33 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     // dV and dK of this KV tile are complete once the last dq_full has fired
     const int tk = j * TS + r;
     if (ok) {
-      __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD;
+      __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD + half * 32;
       __nv_bfloat16* dv_row = dk_row + p.C;
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(t_lane + DV_COL + half * 32, v);
+      tmem_ld_wait();
+      if (tk < p.T) {
 #pragma unroll
-      for (int ch = 0; ch < HD / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + DV_COL + ch * 32, v);
-        tmem_ld_wait();
-        if (tk < p.T) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-            u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-            u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-            u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-            *reinterpret_cast<uint4*>(dv_row + ch * 32 + q * 8) = u;
-          }
+        for (int q = 0; q < 4; ++q) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+          u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+          u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+          u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+          *reinterpret_cast<uint4*>(dv_row + q * 8) = u;
         }
-        tmem_ld_32x32b_x32(t_lane + DK_COL + ch * 32, v);
-        tmem_ld_wait();
-        if (tk < p.T) {
+      }
+      tmem_ld_32x32b_x32(t_lane + DK_COL + half * 32, v);
+      tmem_ld_wait();
+      if (tk < p.T) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]) * p.scale, __uint_as_float(v[q * 8 + 1]) * p.scale);
-            u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]) * p.scale, __uint_as_float(v[q * 8 + 3]) * p.scale);
-            u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]) * p.scale, __uint_as_float(v[q * 8 + 5]) * p.scale);
-            u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]) * p.scale, __uint_as_float(v[q * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(dk_row + ch * 32 + q * 8) = u;
-          }
+        for (int q = 0; q < 4; ++q) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]) * p.scale, __uint_as_float(v[q * 8 + 1]) * p.scale);
+          u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]) * p.scale, __uint_as_float(v[q * 8 + 3]) * p.scale);
+          u.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]) * p.scale, __uint_as_float(v[q * 8 + 5]) * p.scale);
+          u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]) * p.scale, __uint_as_float(v[q * 8 + 7]) * p.scale);
+          *reinterpret_cast<uint4*>(dk_row + q * 8) = u;
         }
       }
     }
@@ -325,36 +345,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; also clears the fp32 dQ rows.
+// stats[0][bh][t] = lse[bh][t] * log2(e); stats[1][bh][t] = sum_d dO[b,t,h,d] * O[b,t,h,d];
+// both zero for T <= t < Tpad. Also clears the fp32 dQ rows.
+// Eight threads share one (row, head): each takes 16 bytes of O and dO, so a warp reads four
+// contiguous 128-byte segments per instruction.
 __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
-                                      const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
-                                      float* __restrict__ dq_accum, int B, int T, int H) {
-  const long long total = (long long)B * T * H;
-  const int C = H * HD;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const int hh = (int)(idx % H);
-    const long long m = idx / H;
-    const __nv_bfloat16* o = out + m * C + hh * HD;
-    const __nv_bfloat16* d = dout + m * C + hh * HD;
-    float* dq = dq_accum + m * C + hh * HD;
-    float s = 0.f;
+                                      const __nv_bfloat16* __restrict__ dout,
+                                      const float* __restrict__ lse, float* __restrict__ stats,
+                                      float* __restrict__ dq_accum, int B, int T, int H, int Tpad) {
+  const long long total = (long long)B * T * H * 8;
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool valid = idx < total;  // every lane stays until after the shuffles
+  const int q = (int)(idx & 7);
+  const long long mh = idx >> 3;  // == m * H + hh, and O / dO / dQ rows are contiguous in it
+  float s = 0.f;
+  if (valid) {
+    const uint4 a = *reinterpret_cast<const uint4*>(out + mh * HD + q * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dout + mh * HD + q * 8);
+    const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* cw = reinterpret_cast<const uint32_t*>(&c);
 #pragma unroll
-    for (int q = 0; q < HD / 8; ++q) {
-      uint4 a = *reinterpret_cast<const uint4*>(o + q * 8);
-      uint4 c = *reinterpret_cast<const uint4*>(d + q * 8);
-      const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
-      const uint32_t* cw = reinterpret_cast<const uint32_t*>(&c);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float2 x = unpack_bf16x2(aw[e]), y = unpack_bf16x2(cw[e]);
-        s += x.x * y.x + x.y * y.y;
-      }
-      reinterpret_cast<float4*>(dq)[q * 2] = make_float4(0.f, 0.f, 0.f, 0.f);
-      reinterpret_cast<float4*>(dq)[q * 2 + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int e = 0; e < 4; ++e) {
+      float2 x = unpack_bf16x2(aw[e]), y = unpack_bf16x2(cw[e]);
+      s += x.x * y.x + x.y * y.y;
     }
+    float* dq = dq_accum + mh * HD + q * 8;
+    reinterpret_cast<float4*>(dq)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(dq)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (valid && q == 0) {
+    const int hh = (int)(mh % H);
+    const long long m = mh / H;
     const int bb = (int)(m / T), t = (int)(m % T);
-    delta[((long long)bb * H + hh) * T + t] = s;
+    const long long bhh = (long long)bb * H + hh;
+    stats[bhh * Tpad + t] = lse[bhh * T + t] * 1.4426950408889634f;
+    stats[((long long)B * H + bhh) * Tpad + t] = s;
+  }
+  // the padding of every stats row must read as zero
+  if (Tpad > T) {
+    const int pad = Tpad - T;
+    const long long npad = 2LL * B * H * pad;
+    if (idx < npad) {
+      const long long row = idx / pad;
+      stats[row * Tpad + T + (int)(idx % pad)] = 0.f;
+    }
   }
 }
 
@@ -382,26 +419,30 @@ __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
 }  // namespace
 
 int flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
-              float* dq_accum, float* delta, int B, int T, int H, int* status, cudaStream_t stream) {
+              float* dq_accum, float* stats, int B, int T, int H, int* status, cudaStream_t stream) {
   const int C = H * HD;
   if (B <= 0 || T <= 0) return 0;
+  const int Tpad = (T + TS - 1) / TS * TS;
   CUtensorMap tm_qkv, tm_do;
   if (!make_tma_2d_bf16(&tm_qkv, qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, HD, kSwizzle128)) return 2;
   if (!make_tma_2d_bf16(&tm_do, dout, (uint64_t)B * T, C, C, 128, HD, kSwizzle128)) return 2;
   {
-    const long long total = (long long)B * T * H;
+    long long total = (long long)B * T * H * 8;
+    const long long npad = 2LL * B * H * (Tpad - T);
+    if (npad > total) total = npad;
     const int grid = (int)((total + 255) / 256);
     flash_bwd_prep_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
-                                                  delta, dq_accum, B, T, H);
+                                                  lse, stats, dq_accum, B, T, H, Tpad);
   }
   BwdParams p;
-  p.lse = lse; p.delta = delta;
+  p.stats = stats; p.Tpad = Tpad;
   p.dqkv = (__nv_bfloat16*)dqkv;
   p.dq_accum = dq_accum;
   p.B = B; p.T = T; p.H = H; p.C = C;
   p.scale = 0.125f;
   p.scale_log2 = 0.125f * 1.4426950408889634f;
   p.status = status;
+  p.debug = getenv("Z2H_FLASH_DEBUG") ? atoi(getenv("Z2H_FLASH_DEBUG")) : 0;
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -420,9 +461,12 @@ int flash_bwd(const void* qkv, const void* out, const void* dout, const float* l
 
 }  // namespace z2h
 
+extern "C" int z2h_flash_bwd_stats_elems(int B, int T, int H) {
+  return 2 * B * H * ((T + 127) / 128 * 128);
+}
 extern "C" int z2h_flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
-                             void* dqkv, float* dq_accum, float* delta, int B, int T, int H,
+                             void* dqkv, float* dq_accum, float* stats, int B, int T, int H,
                              int* status, void* stream) {
-  return z2h::flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, delta, B, T, H, status,
+  return z2h::flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, status,
                         (cudaStream_t)stream);
 }

@@ -8,10 +8,11 @@
 //
 // One CTA handles 128 query rows of one (batch, head) and walks the KV tiles 0..diagonal:
 //   warp 0     TMA: Q once, K/V tiles through a 2-stage ring (128-byte swizzle)
-//   warp 1     tcgen05.mma: S = Q K^T (128x128x64) into TMEM, then O_j = P V (128x64x128)
+//   warp 1     tcgen05.mma: S = Q K^T (128x128x64) into TMEM, then O += P V (128x64x128)
 //   warps 2-5  one query row per thread: read S from TMEM, online softmax in fp32 (no
 //              shuffles: a thread owns its row), write P as bf16 into swizzled shared memory
-//              for the second MMA, then fold O_j into the register accumulator.
+//              for the second MMA. O accumulates in TMEM across KV tiles and is rescaled
+//              there only when a row maximum grows by more than 2^8.
 // TMEM use is 192 columns (allocated as 256) and shared memory ~113 KiB, so two CTAs share an
 // SM and one CTA's tensor-core work overlaps the other's exponentials.
 #include "../common/ptx.cuh"
@@ -82,7 +83,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);
     mbar_init(pv_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -120,16 +121,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(QT, KT, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(QT, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      // descriptors are built once; inside the loop an MMA costs one 64-bit add per operand
+      const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t p_desc = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
+      uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
+#pragma unroll
+      for (int s = 0; s < KV_STAGES; ++s) {
+        k_desc[s] = make_smem_desc_sw128(smem_u32(sK + s * TILE_BYTES), 16, 1024);
+        v_desc[s] = make_smem_desc_sw128(smem_u32(sV + s * TILE_BYTES), 16, 1024);
+      }
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
       if (ok) ok = mbar_wait_bounded(&k_full[0], 0, abort_flag, p.status, kTimeoutFull);
       if (ok) {
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          tc_mma_f16_ss(tmem_base + S_COL, make_smem_desc_sw128(q_addr + k * 32, 16, 1024),
-                        make_smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+          tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(k_desc[0], k * 32),
+                        idesc_s, k > 0);
         tc_commit(s_full);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
@@ -138,25 +146,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
         if (!mbar_wait_bounded(&v_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+        const uint64_t vd = s == 0 ? v_desc[0] : v_desc[1];
 #pragma unroll
         for (int k = 0; k < KT / 16; ++k) {
-          const uint32_t pa = p_addr + (k >> 2) * (QT * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + PV_COL, make_smem_desc_sw128(pa, 16, 1024),
-                        make_smem_desc_sw128(v_addr + k * 2048, 16, 1024), idesc_pv, k > 0);
+          tc_mma_f16_ss(tmem_base + PV_COL,
+                        desc_advance(p_desc, (k >> 2) * (QT * 128) + (k & 3) * 32),
+                        desc_advance(vd, k * 2048), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(pv_full);
+        if (j == n_kv - 1) tc_commit(pv_full);
         tc_commit(&kv_empty[s]);
         if (j + 1 < n_kv) {
           const int s2 = (j + 1) % KV_STAGES;
           const uint32_t ph2 = ((j + 1) / KV_STAGES) & 1;
           if (!mbar_wait_bounded(&k_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
           tc_fence_after();
-          const uint32_t k_addr = smem_u32(sK + s2 * TILE_BYTES);
+          const uint64_t kd = s2 == 0 ? k_desc[0] : k_desc[1];
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k)
-            tc_mma_f16_ss(tmem_base + S_COL, make_smem_desc_sw128(q_addr + k * 32, 16, 1024),
-                          make_smem_desc_sw128(k_addr + k * 32, 16, 1024), idesc_s, k > 0);
+            tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(kd, k * 32),
+                          idesc_s, k > 0);
           tc_commit(s_full);
         }
       }
@@ -165,10 +173,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // query row within the tile == TMEM lane
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    // m_run is the maximum the stored O / l are expressed against. It only moves when the row
+    // maximum grows by more than 2^8 (in the exp2 domain), so O, which accumulates in TMEM
+    // across KV tiles, rarely needs rescaling; P stays <= 2^8, well inside bf16 / fp32 range.
     float m_run = -INFINITY, l_run = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
     const uint32_t p_row = smem_u32(sP) + r * 128;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
@@ -178,65 +186,98 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       }
       tc_fence_after();
       const bool diag = (j == qi);
-      float m_new = m_run;
-#pragma unroll 1
-      for (int ch = 0; ch < KT / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, v);
-        tmem_ld_wait();
+      // the whole score row (128 fp32) comes into registers with one wait
+      uint32_t sv[KT / 32][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = __uint_as_float(v[i]);
-          if (!diag || ch * 32 + i <= r) m_new = fmaxf(m_new, x);
-        }
-      }
-      const float mc = m_new * p.scale_log2;
-      const float alpha = exp2f(m_run * p.scale_log2 - mc);  // exp2(-inf) == 0 on the first tile
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < KT / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      for (int ch = 0; ch < KT / 32; ++ch) tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, sv[ch]);
+      tmem_ld_wait();
+      float m_new = m_run;
+      if (!diag) {
+        float m0 = m_new, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - mc);
-          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - mc);
-          if (diag) {
-            if (ch * 32 + i > r) p0 = 0.f;
-            if (ch * 32 + i + 1 > r) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
+          m0 = max3(m0, __uint_as_float(sv[0][i]), __uint_as_float(sv[0][i + 1]));
+          m1 = max3(m1, __uint_as_float(sv[1][i]), __uint_as_float(sv[1][i + 1]));
+          m2 = max3(m2, __uint_as_float(sv[2][i]), __uint_as_float(sv[2][i + 1]));
+          m3 = max3(m3, __uint_as_float(sv[3][i]), __uint_as_float(sv[3][i + 1]));
         }
+        m_new = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < KT / 32; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (ch * 32 + i <= r) m_new = fmaxf(m_new, __uint_as_float(sv[ch][i]));
+      }
+      if (j == 0) {
+        m_run = m_new;  // nothing accumulated yet
+      } else {
+        // s_full(j) was committed after P V of tile j-1, so O in TMEM is complete here
+        const bool grow = (m_new - m_run) * p.scale_log2 > 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2_fast((m_run - m_new) * p.scale_log2) : 1.f;
+#pragma unroll
+          for (int q = 0; q < HD / 16; ++q) {
+            uint32_t ov[16];
+            tmem_ld_32x32b_x16(t_lane + PV_COL + q * 16, ov);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_32x32b_x16(t_lane + PV_COL + q * 16, ov);
+          }
+          tmem_st_wait();
+          if (grow) {
+            l_run *= alpha;
+            m_run = m_new;
+          }
+        }
+      }
+      const float mc = m_run * p.scale_log2;
+      // p = 2^(s * c - m * c), row sum, bf16 P into swizzled shared memory
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < KT / 32; ++ch) {
         // 32 columns = four 16-byte chunks of this row inside swizzle atom (ch >> 1)
         const uint32_t atom = p_row + (ch >> 1) * (QT * 128);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = q * 8 + e * 2;
+            float p0 = ex2_fast(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -mc));
+            float p1 = ex2_fast(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -mc));
+            if (diag) {
+              if (ch * 32 + i > r) p0 = 0.f;
+              if (ch * 32 + i + 1 > r) p1 = 0.f;
+            }
+            rs0 += p0;
+            rs1 += p1;
+            pk[e] = pack_bf16x2(p0, p1);
+          }
           const uint32_t chunk = (uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(atom + chunk * 16),
-                       "r"(pk[q * 4 + 0]), "r"(pk[q * 4 + 1]), "r"(pk[q * 4 + 2]), "r"(pk[q * 4 + 3])
+                       "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                        : "memory");
         }
       }
-      l_run = l_run * alpha + rowsum;
-      m_run = m_new;
+      l_run += rs0 + rs1;
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_full);
-      if (!mbar_wait_bounded(pv_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);  // one arrival per softmax warp
+    }
+    if (ok && !mbar_wait_bounded(pv_full, 0, abort_flag, p.status, kTimeoutTmemFull)) ok = false;
+    tc_fence_after();
+    float o[HD];
+    if (ok) {
 #pragma unroll
-      for (int ch = 0; ch < HD / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + PV_COL + ch * 32, v);
+      for (int q = 0; q < HD / 32; ++q) {
+        uint32_t ov[32];
+        tmem_ld_32x32b_x32(t_lane + PV_COL + q * 32, ov);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[ch * 32 + i] = o[ch * 32 + i] * alpha + __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) o[q * 32 + i] = __uint_as_float(ov[i]);
       }
     }
     const int t = qi * QT + r;

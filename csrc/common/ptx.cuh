@@ -223,6 +223,23 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// A descriptor for the same matrix `byte_offset` further on in shared memory (the caller keeps
+// the sum inside the 14-bit address field, i.e. inside the CTA's shared memory window).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_offset) {
+  return desc + (uint64_t)(byte_offset >> 4);
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier. Addresses and size must be
+// multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                             uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread i <-> lane i of
 // the warp's TMEM lane quarter).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -285,6 +302,19 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float t = tanh_fast(u);
   float du = k0 * (1.0f + 3.0f * k1 * x2);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+// 2^x on the special-function unit, one instruction (flush-to-zero, no range fix-up).
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -201,18 +201,28 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
-__global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int num_partials,
-                                            float* __restrict__ dw, float* __restrict__ db, int C,
-                                            int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float sw = 0.f, sb = 0.f;
-  for (int p = 0; p < num_partials; ++p) {
-    sw += scratch[(long long)p * 2 * C + c];
-    sb += scratch[(long long)p * 2 * C + C + c];
+// Folds the per-CTA partial rows in a fixed order: a CTA owns 32 columns of the [2, C] row
+// (dw then db) and its 32 warps-worth of threads split the partials 32 ways, then a shared-memory
+// tree in fixed order finishes the sum.
+__global__ void __launch_bounds__(1024)
+layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int num_partials,
+                            float* __restrict__ dw, float* __restrict__ db, int C, int accumulate) {
+  __shared__ float sh[32][33];
+  const int col_in = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int c2 = blockIdx.x * 32 + col_in;  // column of the [2C] partial row
+  float s = 0.f;
+  if (c2 < 2 * C)
+    for (int p = part; p < num_partials; p += 32) s += scratch[(long long)p * 2 * C + c2];
+  sh[part][col_in] = s;
+  __syncthreads();
+  if (part == 0 && c2 < 2 * C) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += sh[k][col_in];
+    float* dst = c2 < C ? dw : db;
+    const int c = c2 < C ? c2 : c2 - C;
+    if (dst != nullptr) dst[c] = accumulate ? dst[c] + t : t;
   }
-  if (dw != nullptr) dw[c] = accumulate ? dw[c] + sw : sw;
-  if (db != nullptr) db[c] = accumulate ? db[c] + sb : sb;
 }
 
 }  // namespace
@@ -263,8 +273,8 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
   else if (C <= 1024) { if (has_db) Z2H_LN_BWD(4, true); else Z2H_LN_BWD(4, false); }
   else { if (has_db) Z2H_LN_BWD(8, true); else Z2H_LN_BWD(8, false); }
 #undef Z2H_LN_BWD
-  layernorm_bwd_reduce_kernel<<<(C + 255) / 256, 256, 0, stream>>>(scratch, grid, dw, db, C,
-                                                                 accumulate);
+  layernorm_bwd_reduce_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(scratch, grid, dw, db, C,
+                                                                    accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

@@ -5,7 +5,7 @@
 namespace z2h {
 
 // Upper bound on the number of CTAs (= partial rows in the scratch buffer) of the backward.
-constexpr int kLayerNormBwdMaxCtas = 592;  // 4 per SM on a 148-SM part
+constexpr int kLayerNormBwdMaxCtas = 296;  // 2 per SM on a 148-SM part
 
 // Number of partial rows the backward writes for M rows; scratch must hold
 // num_partials * 2 * C floats.

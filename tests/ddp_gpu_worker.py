@@ -1,0 +1,87 @@
+"""Per-rank body of the multi-GPU tests (NCCL for rendezvous, NVLS off, own kernels on P2P)."""
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+import torch.distributed as dist
+
+
+def rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-12)
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from zero_to_hero_b200.config import get_preset
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+    from zero_to_hero_b200.ops import _lib
+    from zero_to_hero_b200.parallel.fused_ddp import (BF16, F32, ONE_SHOT, TWO_SHOT, FusedDDP, PeerComm,
+                                                      SymmetricBuffer, TorchDDPComm)
+
+    # ---- standalone all-reduce, one- and two-shot, fp32 and bf16, against NCCL
+    comm = PeerComm(dev)
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (256, 4096 + 64, 1 << 20, (1 << 22) + 128):
+            buf = SymmetricBuffer(n, dtype, dev)
+            torch.manual_seed(100 + rank)
+            x = (torch.randn(n, device=dev) * 0.1).to(dtype)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            for algo in (ONE_SHOT, TWO_SHOT):
+                buf.tensor.copy_(x)
+                torch.cuda.synchronize()
+                dist.barrier()
+                out = comm.allreduce_(buf, algo=algo)
+                torch.cuda.synchronize()
+                _lib.check_status(dev)
+                tol = 1e-5 if dtype == torch.float32 else 2e-2
+                assert rel(out, ref) < tol, (dtype, n, algo, rel(out, ref))
+                dist.barrier()
+    if rank == 0:
+        print("allreduce OK", flush=True)
+
+    # ---- fused reduce-scatter + AdamW + all-gather against NCCL all-reduce + local AdamW
+    cfg = get_preset("gpt2-tiny")
+    cfg.model.emb_dim, cfg.model.num_heads, cfg.model.num_layers = 128, 2, 2
+    cfg.model.vocab_size, cfg.model.block_size = 512, 128
+    cfg.train.micro_batch = 2
+    cfg.optim.warmup_steps, cfg.optim.schedule, cfg.optim.lr_max = 0, "constant", 1e-3
+    engines = [GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev), seed=7),
+               GPT2TrainEngine(cfg, dev, comm=TorchDDPComm(dev), seed=7)]
+    g = torch.Generator().manual_seed(1000 + rank)  # every rank trains on different data
+    for step in range(4):
+        batches = []
+        for _ in range(2):
+            tok = torch.randint(0, 512, (2 * 128 + 1,), generator=g)
+            batches.append((tok[:-1].view(2, 128).pin_memory(), tok[1:].view(2, 128).pin_memory()))
+        res = []
+        for e in engines:
+            e.train_step(batches, lr=1e-3)
+            res.append((e.read_loss(), e.read_grad_norm()))
+        _lib.check_status(dev)
+        (l0, n0), (l1, n1) = res
+        assert abs(l0 - l1) < 1e-3, (step, l0, l1)
+        assert abs(n0 - n1) / n1 < 1e-3, (step, n0, n1)
+        a, b = engines[0].full_master(), engines[1].full_master()
+        assert rel(a, b) < 1e-3, (step, rel(a, b))
+        # every rank holds the same bf16 working copy after the all-gather
+        w = engines[0].p16.float()
+        ref = w.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(w, ref), "bf16 replicas differ"
+    if rank == 0:
+        print("fused ddp OK", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"OK rank {rank}", flush=True)
+
+
+if __name__ == "__main__":
+    main()

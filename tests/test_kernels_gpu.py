@@ -119,8 +119,8 @@ def test_flash_attention_fwd_bwd(dev, B, T, H):
     refd = torch.cat([g.grad.transpose(1, 2).reshape(B * T, C) for g in (q, k, v)], 1)
     dqkv = torch.zeros_like(qkv)
     dqa = torch.empty(B * T, C, device=dev)
-    delta = torch.empty(B, H, T, device=dev)
-    N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, delta, B, T, H)
+    stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
+    N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, stats, B, T, H)
     status_ok()
     for i, name in enumerate("qkv"):
         assert rel_err(dqkv[:, i * C:(i + 1) * C], refd[:, i * C:(i + 1) * C]) < 2e-2, name
@@ -266,3 +266,32 @@ def test_colsum_and_cast(dev):
     N.cast_f32_to_bf16(x, y)
     assert torch.equal(y, x.bfloat16())
     status_ok()
+
+
+# ------------------------------------------------------------------- bounded device waits
+def test_bounded_peer_wait_times_out_with_status_and_context_survives(dev):
+    """A wait on a flag nobody sets must end by itself, report kTimeoutPeer, and leave the
+    context usable; a flag that is set lets the wait succeed."""
+    import ctypes
+    from zero_to_hero_b200.ops import _lib
+    lib = _lib.cuda_lib()
+    lib.z2h_wait_probe.restype = ctypes.c_int
+    lib.z2h_wait_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint,
+                                   ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    pad = torch.zeros(64, dtype=torch.int64, device=dev)
+    result = torch.full((1,), -1, dtype=torch.int32, device=dev)
+    status = _lib.status_word(dev)
+    rc = lib.z2h_wait_probe(_lib.ptr(pad), 0, 1, 5, 50_000_000, _lib.ptr(status), _lib.ptr(result),
+                            _lib.stream_ptr())  # 50 ms budget, epoch 5 never arrives
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(result.item()) == 0
+    with pytest.raises(RuntimeError, match="peer"):
+        _lib.check_status(dev)
+    pad[1] = 5 << 32  # slot (kind 0, src 1) now carries epoch 5
+    rc = lib.z2h_wait_probe(_lib.ptr(pad), 0, 1, 5, 50_000_000, _lib.ptr(status), _lib.ptr(result),
+                            _lib.stream_ptr())
+    torch.cuda.synchronize()
+    assert rc == 0 and int(result.item()) == 1
+    _lib.check_status(dev)
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0  # the context still works

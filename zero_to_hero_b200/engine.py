@@ -246,7 +246,7 @@ class GPT2TrainEngine:
         self.d_4c = buf(M, 4 * C)
         self.d_qkv = buf(M, 3 * C)
         self.dq_accum = buf(M, C, dtype=f32)
-        self.delta = buf(B, H, T, dtype=f32)
+        self.attn_stats = buf(N.flash_bwd_stats_elems(B, T, H), dtype=f32)
         self.ln_scratch = buf(N.layernorm_bwd_num_partials(M) * 2 * C, dtype=f32)
 
     # ------------------------------------------------------------------ kernels schedule
@@ -333,7 +333,7 @@ class GPT2TrainEngine:
             N.colsum_bf16(self.d_resid, gw(p + "attn.c_proj.bias"))
             G.gemm(self.d_resid, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
             N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
-                        self.delta, B, T, H)
+                        self.attn_stats, B, T, H)
             self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
             N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)

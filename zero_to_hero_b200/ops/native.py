@@ -127,7 +127,13 @@ def flash_fwd(qkv, out, lse, B, T, H):
                                ptr(_lib.status_word(out.device)), stream_ptr()), "flash_fwd")
 
 
-def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, delta, B, T, H):
+def flash_bwd_stats_elems(B: int, T: int, H: int) -> int:
+    """Number of fp32 scratch elements `flash_bwd` needs for its per-row statistics."""
+    return 2 * B * H * ((T + 127) // 128 * 128)
+
+
+def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H):
+    assert stats.numel() >= flash_bwd_stats_elems(B, T, H)
     _check(_f("z2h_flash_bwd")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), ptr(dq_accum),
-                               ptr(delta), B, T, H, ptr(_lib.status_word(out.device)),
+                               ptr(stats), B, T, H, ptr(_lib.status_word(out.device)),
                                stream_ptr()), "flash_bwd")

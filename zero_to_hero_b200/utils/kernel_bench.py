@@ -101,8 +101,8 @@ def bench_flash(a, dev, which):
         dout = torch.randn_like(out)
         dqkv = torch.empty_like(qkv)
         dqa = torch.empty(B * T, C, device=dev)
-        delta = torch.empty(B, H, T, device=dev)
-        ms = time_kernel(lambda: N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, delta, B, T, H), a.iters,
+        stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
+        ms = time_kernel(lambda: N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, stats, B, T, H), a.iters,
                          flush=not a.no_flush)
         report(f"flash_bwd B{B} T{T} H{H} (3 launches)", ms, flops=2.5 * fl)
     if a.compare:
