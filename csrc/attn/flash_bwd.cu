@@ -35,9 +35,11 @@ constexpr int Q_STAGES = 2;
 constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps
 constexpr int NUM_COMPUTE = 256;
 constexpr int TMEM_COLS = 512;
-constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384;
+constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384;  // dQ: 2 x 64 columns
+constexpr int P_BUFS = 2;  // P^T / dS^T are double-buffered in shared memory
 constexpr int SMEM_BYTES =
-    1024 + 2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + 2 * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
+    2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + 2 * P_BUFS * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
 struct BwdParams {
   const float* stats;  // [2][B*H][Tpad]: lse * log2(e), then delta; zero beyond T
@@ -53,16 +55,18 @@ struct BwdParams {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                  const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint8_t* sK = smem;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (smem_u32(smem_raw) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
+    return;
+  }
+  uint8_t* sK = smem_raw;
   uint8_t* sV = sK + TILE_BYTES;
   uint8_t* sQ = sV + TILE_BYTES;
   uint8_t* sdO = sQ + Q_STAGES * TILE_BYTES;
   uint8_t* sPt = sdO + Q_STAGES * TILE_BYTES;
-  uint8_t* sdSt = sPt + PT_BYTES;
-  float* sLse = reinterpret_cast<float*>(sdSt + PT_BYTES);  // [Q_STAGES][TS], already * log2(e)
+  uint8_t* sdSt = sPt + P_BUFS * PT_BYTES;
+  float* sLse = reinterpret_cast<float*>(sdSt + P_BUFS * PT_BYTES);  // [Q_STAGES][TS], already * log2(e)
   float* sDelta = sLse + Q_STAGES * TS;                      // [Q_STAGES][TS]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + Q_STAGES * TS);
   uint64_t* kv_full = bars;
@@ -165,31 +169,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         tc_fence_after();
         issue_st(0);
       }
+      // Software pipeline: as soon as P^T / dS^T of tile `it` are in shared memory, S^T / dP^T of
+      // tile it+1 are issued first (their TMEM columns were just drained), then the three
+      // products that consume tile `it`; the compute warps meanwhile read dQ of tile it-1 and
+      // start on tile it+1 while those products are still running.
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % Q_STAGES;
+        const uint32_t pb = (it & 1) * PT_BYTES;
         if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
-        tc_fence_after();
-        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
-        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
-#pragma unroll
-        for (int k = 0; k < TS / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + DV_COL, desc_advance(pt_desc, a_off), desc_advance(dod, k * 2048),
-                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < TS / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * (TS * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
-                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < TS / 16; ++k) {
-          tc_mma_f16_ss(tmem_base + DQ_COL, desc_advance(dst_mn_desc, k * 2048),
-                        desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
-        }
-        tc_commit(dq_full);
-        tc_commit(&qdo_empty[s]);
         if (it + 1 < n_iter) {
           const int s2 = (it + 1) % Q_STAGES;
           const uint32_t ph2 = ((it + 1) / Q_STAGES) & 1;
@@ -197,6 +184,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           tc_fence_after();
           issue_st(s2);
         }
+        tc_fence_after();
+        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
+        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          const uint32_t a_off = pb + (k >> 2) * (TS * 128) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + DV_COL, desc_advance(pt_desc, a_off), desc_advance(dod, k * 2048),
+                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          const uint32_t a_off = pb + (k >> 2) * (TS * 128) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
+                        idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < TS / 16; ++k) {
+          tc_mma_f16_ss(tmem_base + DQ_COL + (it & 1) * HD, desc_advance(dst_mn_desc, pb + k * 2048),
+                        desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
+        }
+        tc_commit(dq_full);
+        tc_commit(&qdo_empty[s]);
       }
     }
   } else {
@@ -208,6 +217,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t pt_row = smem_u32(sPt) + half * (TS * 128) + r * 128;
     const uint32_t dst_row = smem_u32(sdSt) + half * (TS * 128) + r * 128;
+    // dQ of tile `t` (TMEM lane == query row; this warp takes 32 of the 64 columns) is added to
+    // the fp32 accumulation buffer; the MMA issuer alternates between two dQ accumulators
+    auto drain_dq = [&](int t) {
+      tc_fence_after();
+      const int tq = (j + t) * TS + r;
+      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD + half * 32;
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(t_lane + DQ_COL + (t & 1) * HD + half * 32, v);
+      tmem_ld_wait();
+      if (tq < p.T && !(p.debug & 1)) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 4),
+                       "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
+                       "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
+                       : "memory");
+        }
+      }
+      tc_fence_before();
+    };
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int i = j + it;
@@ -222,6 +251,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         break;
       }
       tc_fence_after();
+      const uint32_t pb = (it & 1) * PT_BYTES;  // which P^T / dS^T buffer this tile uses
       const bool diag = (i == j);
       const int q_valid = p.T - i * TS;  // columns >= q_valid are past the end of the sequence
       const bool fast = !diag && q_valid >= TS;  // no masking anywhere in this tile
@@ -266,41 +296,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           }
           // 8 columns = one 16-byte chunk of this row inside swizzle atom `half`
           const uint32_t chunk = ((uint32_t)(ch * 4 + q) ^ (uint32_t)(r & 7)) * 16;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + chunk), "r"(pk[0]),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + pb + chunk), "r"(pk[0]),
                        "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                        : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + chunk), "r"(dk[0]),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + pb + chunk), "r"(dk[0]),
                        "r"(dk[1]), "r"(dk[2]), "r"(dk[3])
                        : "memory");
         }
+      }
+      // The products of tile it-1 must have completed before this warp signals tile `it`: a later
+      // wait could otherwise see the barrier two phases ahead and mistake the parity.
+      if (it > 0 && !mbar_wait_bounded(dq_full, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
       }
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);  // one arrival per compute warp
-      if (!mbar_wait_bounded(dq_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      // dQ tile: TMEM lane == query row of tile i; this warp takes 32 of the 64 columns
-      const int tq = i * TS + r;
-      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD + half * 32;
-      {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_lane + DQ_COL + half * 32, v);
-        tmem_ld_wait();
-        if (tq < p.T && !(p.debug & 1)) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 4),
-                         "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
-                         "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
-                         : "memory");
-          }
-        }
-      }
-      tc_fence_before();
+      // while the tensor cores work on this tile, fold dQ of the previous one into global memory
+      if (it > 0) drain_dq(it - 1);
+    }
+    if (ok && n_iter > 0) {
+      ok = mbar_wait_bounded(dq_full, (n_iter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
+      if (ok) drain_dq(n_iter - 1);
     }
     // dV and dK of this KV tile are complete once the last dq_full has fired
     const int tk = j * TS + r;

@@ -37,6 +37,15 @@ struct GemmArgs {
 };
 
 // Returns 0 on success, 1 bad argument, 2 tensor-map encoding failed, 3 launch failed.
+// Validates the arguments and picks the kernel (see gemm_set_algo).
 int gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+
+// The CTA-pair kernel (256 x 256 tiles, tcgen05.mma.cta_group::2); arguments already validated.
+int gemm_bf16_pair(const GemmArgs& args, cudaStream_t stream);
+
+// 0: always the one-CTA kernel (128 x 256 tiles); 1: the CTA-pair kernel whenever M >= 256;
+// 2 (default): CTA pairs when the problem has at least one 256 x 256 tile per pair of SMs.
+void gemm_set_algo(int algo);
+int gemm_get_algo();
 
 }  // namespace z2h

@@ -24,25 +24,15 @@ struct KernelParams {
 
 // Epilogue for 32 consecutive columns of one output row.
 __device__ __forceinline__ void epilogue_chunk(const KernelParams& p, float (&v)[32], long long grow,
-                                               int gcol) {
+                                               int gcol, const float* sbias) {
   const int ncols = min(32, p.N - gcol);
   if (ncols <= 0) return;
   const bool full = (ncols == 32);
-  if (p.bias != nullptr) {
-    if (full) {
-      const uint4* bp = reinterpret_cast<const uint4*>(p.bias + gcol);
+  if (sbias != nullptr) {  // bias of these 32 columns, staged in shared memory (zero past N)
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 b = __ldg(bp + q);
-        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
-               f3 = unpack_bf16x2(b.w);
-        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
-        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
-      }
-    } else {
-      #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) v[j] += __bfloat162float(p.bias[gcol + j]);
+    for (int j = 0; j < 32; j += 4) {
+      const float4 b = *reinterpret_cast<const float4*>(sbias + j);
+      v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
     }
   }
   if (p.epi == kEpiResidual) {
@@ -166,6 +156,20 @@ __device__ __forceinline__ void epilogue_chunk(const KernelParams& p, float (&v)
   }
 }
 
+
+// Each epilogue warp copies the bias of the 128 columns it will drain into its own 128-float
+// slice of shared memory (lane l takes columns 4l..4l+3), so that the per-chunk epilogue reads
+// it with broadcast loads instead of waiting on global memory. Only a warp-level sync is needed.
+__device__ __forceinline__ void stage_bias(const KernelParams& p, float* my_sbias, int gcol0, int lane) {
+  if (p.bias == nullptr) return;
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = gcol0 + lane * 4 + j;
+    my_sbias[lane * 4 + j] = c < p.N ? __bfloat162float(p.bias[c]) : 0.f;
+  }
+  __syncwarp();
+}
 
 inline KernelParams make_kernel_params(const GemmArgs& g) {
   KernelParams p;

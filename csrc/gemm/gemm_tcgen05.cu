@@ -7,7 +7,8 @@
 //   warp 0      TMA producer   cp.async.bulk.tensor 2-D tiles, 128-byte swizzle, 4-stage ring
 //   warp 1      MMA issuer     one elected lane issues tcgen05.mma (128x256x16) and commits
 //                              stage releases / accumulator completions to mbarriers
-//   warps 2-5   epilogue       tcgen05.ld the 128x256 fp32 accumulator (one row per thread),
+//   warps 2-9   epilogue       tcgen05.ld the 128x256 fp32 accumulator (one row per thread, two
+//                              warps per TMEM lane quarter, each taking half of the columns),
 //                              apply bias / GELU / residual / GELU' and store
 //
 // Two accumulators of 256 TMEM columns each are used in turn, so the epilogue of tile i runs
@@ -35,9 +36,10 @@ constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * 128 * 4;
 
 using gemm_detail::KernelParams;
 using gemm_detail::epilogue_chunk;
@@ -57,6 +59,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* sbias_all = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -74,7 +77,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -191,8 +194,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
     }
   } else {
-    // ------------------------------ epilogue (4 warps) ------------------------------
+    // ------------------------------ epilogue (8 warps) ------------------------------
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
@@ -212,23 +216,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_after();
       const long long grow = (long long)mt * BM + row_in_tile;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+      // this warp drains 4 of the 8 column chunks; the next chunk's TMEM load is in flight while
+      // the current one goes through the epilogue
+      const int c0 = half * 4;
+      const int gcol0 = nt * BN + c0 * 32;
+      float* my_sbias = sbias_all + (warp - 2) * 128;
+      gemm_detail::stage_bias(p, my_sbias, gcol0, lane);
+      uint32_t r[2][32];
+      tmem_ld_32x32b_x32(taddr + c0 * 32, r[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         tmem_ld_wait();
-        if (chunk == BN / 32 - 1) {
-          // the accumulator is in registers now: hand it back to the MMA issuer
+        if (c + 1 < 4) tmem_ld_32x32b_x32(taddr + (c0 + c + 1) * 32, r[(c + 1) & 1]);
+        if (c == 3) {
+          // the accumulator part this warp owns is in registers now: hand it back
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tempty_bar[acc]);
         }
-        const int gcol = nt * BN + chunk * 32;
+        const int gcol = gcol0 + c * 32;
         if (grow < p.M && gcol < p.N && !empty_split) {
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          epilogue_chunk(p, v, grow, gcol);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[c & 1][j]);
+          epilogue_chunk(p, v, grow, gcol, p.bias != nullptr ? my_sbias + c * 32 : nullptr);
         }
       }
     }
@@ -279,6 +290,10 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace
 
+static int g_algo = 2;
+void gemm_set_algo(int algo) { g_algo = algo; }
+int gemm_get_algo() { return g_algo; }
+
 int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   // argument checks: everything the TMA descriptors and the vector epilogue rely on
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
@@ -291,6 +306,11 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   if (g.epi == kEpiResidual && (g.residual == nullptr || (g.ldr % 8))) return 1;
   if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
+  {
+    const long long tiles256 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * (g.split_k < 1 ? 1 : g.split_k);
+    const bool pair = g_algo == 1 ? g.M >= 256 : (g_algo == 2 && g.M >= 256 && tiles256 >= 74);
+    if (pair) return gemm_bf16_pair(g, stream);
+  }
   if (g.a_mn == 0 && g.b_mn == 0) return launch<0, 0>(g, stream);
   if (g.a_mn == 0 && g.b_mn == 1) return launch<0, 1>(g, stream);
   if (g.a_mn == 1 && g.b_mn == 0) return launch<1, 0>(g, stream);
@@ -299,6 +319,8 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace z2h
 
+extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }
+extern "C" int z2h_gemm_get_algo() { return z2h::gemm_get_algo(); }
 extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
                              long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
                              int epi, int split_k, const void* bias, const void* residual,

@@ -1,0 +1,309 @@
+// bf16 GEMM on CTA pairs: C[M,N] = A[M,K] * B[N,K]^T with tcgen05.mma.cta_group::2.
+//
+// Two CTAs of a cluster (two neighbouring SMs) work on one 256 x 256 output tile. Each CTA
+// loads 128 rows of A and 128 of the 256 rows of B per K-block (32 KiB instead of the 48 KiB a
+// lone CTA needs for a 128 x 256 tile), the even CTA issues one MMA of shape 256 x 256 x 16 for
+// both, and each CTA keeps its 128 x 256 half of the fp32 accumulator in its own tensor
+// memory. Per SM this halves the B traffic through shared memory, which is what bounds the
+// one-CTA kernel (128 B/clk per SM against 192 B/clk wanted); a 6-stage ring fits instead of 4.
+//
+// Synchronisation: the "full" barrier of a stage lives in the even CTA and counts the bytes of
+// both CTAs' TMA loads (the odd CTA's loads name that barrier; there is no multicast load,
+// every CTA fetches its own tiles). Stage release and accumulator completion are
+// tcgen05.commit arrivals multicast to the same barrier offset in both CTAs. The epilogue
+// warps of both CTAs arrive on the even CTA's "accumulator drained" barrier.
+// Warp roles, epilogues, split-K and operand layouts are those of gemm_tcgen05.cu.
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+#include "gemm.h"
+#include "gemm_epilogue.cuh"
+
+namespace z2h {
+namespace {
+
+using gemm_detail::KernelParams;
+using gemm_detail::epilogue_chunk;
+
+constexpr int TM = 256;        // tile rows per CTA pair
+constexpr int HM = 128;        // tile rows per CTA
+constexpr int BN = 256;        // tile columns
+constexpr int HN = 128;        // B rows loaded per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = HM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = HN * BK * 2;  // 16 KiB
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * 128 * 4;
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const KernelParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sA = smem_raw;
+  uint8_t* sB = smem_raw + STAGES * A_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + STAGES * B_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* sbias_all = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs), 1 = peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const bool aligned = (smem_u32(smem_raw) & 1023u) == 0;
+
+  const int tiles_m = (p.M + TM - 1) / TM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;
+  const int total_tiles = aligned ? tiles_m * tiles_n * p.split_k : 0;
+  if (!aligned && threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * EPI_WARPS);  // the epilogue warps of both CTAs of the pair
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must exist before any remote arrival or load completion targets them
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (one per CTA) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        const int mt = tile % tiles_m;
+        const int rest = tile / tiles_m;
+        const int nt = rest % tiles_n;
+        const int ks = rest / tiles_n;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        const int m0 = mt * TM + (int)rank * HM;
+        const int n0 = nt * BN + (int)rank * HN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          // the leader's barrier counts the bytes of both CTAs
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (A_MN == 0) {
+            tma_load_2d_pair(a_dst, &tmA, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < HM / 64; ++c)
+              tma_load_2d_pair(a_dst + c * (64 * BK * 2), &tmA, &full_bar[stage], m0 + c * 64, kb * BK);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(b_dst, &tmB, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < HN / 64; ++c)
+              tma_load_2d_pair(b_dst + c * (64 * BK * 2), &tmB, &full_bar[stage], n0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, BN, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t b_lbo = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+        const int rest = tile / tiles_m;
+        const int ks = rest / tiles_n;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, kTimeoutTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
+          const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_f16_ss_2cta(d_tmem, desc_advance(adesc0, k * a_kstep), desc_advance(bdesc0, k * b_kstep),
+                               idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          tc_commit_2cta(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit_2cta(&tfull_bar[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (8 warps per CTA) ------------------------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_in_half = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+      const int mt = tile % tiles_m;
+      const int rest = tile / tiles_m;
+      const int nt = rest % tiles_n;
+      const int ks = rest / tiles_n;
+      const bool empty_split = ks * kb_per_split >= num_kb_total;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long grow = (long long)mt * TM + (long long)rank * HM + row_in_half;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      // this warp drains 4 of the 8 column chunks; the next chunk's TMEM load is in flight while
+      // the current one goes through the epilogue
+      const int c0 = half * 4;
+      const int gcol0 = nt * BN + c0 * 32;
+      float* my_sbias = sbias_all + (warp - 2) * 128;
+      gemm_detail::stage_bias(p, my_sbias, gcol0, lane);
+      uint32_t r[2][32];
+      tmem_ld_32x32b_x32(taddr + c0 * 32, r[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld_32x32b_x32(taddr + (c0 + c + 1) * 32, r[(c + 1) & 1]);
+        if (c == 3) {
+          // the accumulator part this warp owns is in registers now: hand it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);
+        }
+        const int gcol = gcol0 + c * 32;
+        if (grow < p.M && gcol < p.N && !empty_split) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[c & 1][j]);
+          epilogue_chunk(p, v, grow, gcol, p.bias != nullptr ? my_sbias + c * 32 : nullptr);
+        }
+      }
+    }
+  }
+
+  // nobody leaves while the other CTA may still signal or read this CTA's barriers / memory
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int A_MN, int B_MN>
+int launch_pair(const GemmArgs& g, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (A_MN == 0)
+    ok = make_tma_2d_bf16(&tmA, g.A, g.M, g.K, g.lda, HM, BK, kSwizzle128);
+  else
+    ok = make_tma_2d_bf16(&tmA, g.A, g.K, g.M, g.lda, BK, 64, kSwizzle128);
+  if (!ok) return 2;
+  if (B_MN == 0)
+    ok = make_tma_2d_bf16(&tmB, g.B, g.N, g.K, g.ldb, HN, BK, kSwizzle128);
+  else
+    ok = make_tma_2d_bf16(&tmB, g.B, g.K, g.N, g.ldb, BK, 64, kSwizzle128);
+  if (!ok) return 2;
+  const KernelParams p = gemm_detail::make_kernel_params(g);
+
+  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  static int num_sms = 0;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    attr_set = true;
+  }
+  const int tiles = ((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) * p.split_k;
+  int pairs = num_sms / 2;
+  if (g.max_ctas > 0 && pairs > g.max_ctas / 2) pairs = g.max_ctas / 2 > 0 ? g.max_ctas / 2 : 1;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs < 1) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace
+
+int gemm_bf16_pair(const GemmArgs& g, cudaStream_t stream) {
+  if (g.a_mn == 0 && g.b_mn == 0) return launch_pair<0, 0>(g, stream);
+  if (g.a_mn == 0 && g.b_mn == 1) return launch_pair<0, 1>(g, stream);
+  if (g.a_mn == 1 && g.b_mn == 0) return launch_pair<1, 0>(g, stream);
+  return launch_pair<1, 1>(g, stream);
+}
+
+}  // namespace z2h

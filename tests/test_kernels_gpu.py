@@ -295,3 +295,34 @@ def test_bounded_peer_wait_times_out_with_status_and_context_survives(dev):
     assert rc == 0 and int(result.item()) == 1
     _lib.check_status(dev)
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0  # the context still works
+
+
+# ------------------------------------------------------------------------------ sampling
+def test_sample_topk_distribution_and_support(dev):
+    from zero_to_hero_b200.ops.sampling import sample_topk_native
+    V = 1000
+    logits = torch.randn(V, device=dev) * 2
+    rows = logits.repeat(4096, 1)  # every row draws with its own counter
+    ids = sample_topk_native(rows, temperature=0.8, top_k=None, seed=7).view(-1)
+    p = torch.softmax(logits / 0.8, 0)
+    freq = torch.bincount(ids, minlength=V).float() / ids.numel()
+    assert (freq - p).abs().max().item() < 0.02
+    assert freq[p.argmax()].item() == pytest.approx(p.max().item(), abs=0.02)
+    # top-k keeps exactly the k largest (no ties here) and renormalises among them
+    k = 5
+    ids = sample_topk_native(rows, temperature=1.0, top_k=k, seed=11).view(-1)
+    top = torch.topk(logits, k).indices
+    assert set(ids.unique().tolist()) <= set(top.tolist())
+    pk = torch.softmax(logits[top], 0)
+    fk = torch.stack([(ids == t).float().mean() for t in top])
+    assert (fk - pk).abs().max().item() < 0.03
+    # a very low temperature is an arg-max; same seed and offset reproduce
+    assert sample_topk_native(rows[:8], 1e-3, None, 3).view(-1).tolist() == [int(logits.argmax())] * 8
+    a = sample_topk_native(rows[:64], 1.0, 50, seed=5, offset=9)
+    b = sample_topk_native(rows[:64], 1.0, 50, seed=5, offset=9)
+    assert torch.equal(a, b)
+    # ties at the k-th value are all kept, as `logits < kth` masking does
+    t = torch.tensor([[1.0, 3.0, 3.0, 3.0, 0.0]], device=dev).repeat(512, 1)
+    seen = set(sample_topk_native(t, 1.0, 2, seed=1).view(-1).tolist())
+    assert seen == {1, 2, 3}
+    status_ok()

@@ -58,3 +58,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
     if rc != 0:
         raise RuntimeError(f"z2h_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
     return out
+
+
+def set_algo(algo: int) -> None:
+    """0: one-CTA kernel (128x256 tiles); 1: CTA-pair kernel (256x256 tiles, cta_group::2) whenever
+    M >= 256; 2: automatic choice (default)."""
+    _lib.cuda_lib().z2h_gemm_set_algo(int(algo))
+
+
+def get_algo() -> int:
+    return int(_lib.cuda_lib().z2h_gemm_get_algo())
