@@ -20,155 +20,243 @@ struct KernelParams {
   const __nv_bfloat16* aux_in;
   long long ldaux;
   int* status;
+  int wide;  // every row segment the epilogue touches is 32-byte aligned
 };
 
-// Epilogue for 32 consecutive columns of one output row.
-__device__ __forceinline__ void epilogue_chunk(const KernelParams& p, float (&v)[32], long long grow,
-                                               int gcol, const float* sbias) {
-  const int ncols = min(32, p.N - gcol);
-  if (ncols <= 0) return;
-  const bool full = (ncols == 32);
-  if (sbias != nullptr) {  // bias of these 32 columns, staged in shared memory (zero past N)
+__device__ __forceinline__ float4 load_bf16x4(const __nv_bfloat16* ptr) {
+  const uint2 u = *reinterpret_cast<const uint2*>(ptr);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// Floats of shared memory one epilogue warp needs (the bias of its 128 columns).
+constexpr int kEpiBiasFloats = 128;
+
+// ---- 16-byte and 32-byte global accesses -------------------------------------------------
+// A thread owns one accumulator row, i.e. 32 consecutive output columns: 64 contiguous bytes
+// as bf16, 128 as fp32. With 32-byte vectors every request a lane makes is one whole sector,
+// so rows that lie far apart (one row per lane) cost no partial-sector writes; 16-byte
+// vectors remain for pointers or pitches that are only 16-byte aligned.
+__device__ __forceinline__ void ld_global_b128(const void* ptr, uint32_t* w) {
+  asm volatile("ld.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+               : "l"(ptr));
+}
+__device__ __forceinline__ void st_global_b128(void* ptr, const uint32_t* w) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3])
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_b256(const void* ptr, uint32_t* w) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]),
+                 "=r"(w[7])
+               : "l"(ptr));
+}
+__device__ __forceinline__ void st_global_b256(void* ptr, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]),
+               "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+// N_WORDS 32-bit words (a multiple of 8) from / to consecutive addresses
+template <int N_WORDS>
+__device__ __forceinline__ void ld_row(const void* ptr, uint32_t (&w)[N_WORDS], bool wide) {
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(ptr);
+  if (wide) {
+#pragma unroll
+    for (int i = 0; i < N_WORDS / 8; ++i) ld_global_b256(b + i * 32, &w[i * 8]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N_WORDS / 4; ++i) ld_global_b128(b + i * 16, &w[i * 4]);
+  }
+}
+template <int N_WORDS>
+__device__ __forceinline__ void st_row(void* ptr, const uint32_t (&w)[N_WORDS], bool wide) {
+  uint8_t* b = reinterpret_cast<uint8_t*>(ptr);
+  if (wide) {
+#pragma unroll
+    for (int i = 0; i < N_WORDS / 8; ++i) st_global_b256(b + i * 32, &w[i * 8]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N_WORDS / 4; ++i) st_global_b128(b + i * 16, &w[i * 4]);
+  }
+}
+
+// Epilogue of 32 consecutive columns of one output row, all of which exist; one instantiation
+// per epilogue kind and output type keeps each kernel's hot path short.
+//   r: the accumulator values (fp32 bit patterns); sbias: bias of these columns in shared memory.
+template <int EPI, bool OUT_FP32>
+__device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32_t (&r)[32], long long grow,
+                                             int gcol, const float* sbias) {
+  const bool wide = p.wide != 0;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (sbias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-      const float4 b = *reinterpret_cast<const float4*>(sbias + j);
+      const float4 b = *reinterpret_cast<const float4*>(sbias + j);  // same address in all lanes
       v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
     }
   }
-  if (p.epi == kEpiResidual) {
-    const __nv_bfloat16* rp = p.residual + grow * p.ldr + gcol;
-    if (full) {
+  if (EPI == kEpiResidual) {
+    uint32_t w[16];
+    ld_row(p.residual + grow * p.ldr + gcol, w, wide);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 b = *reinterpret_cast<const uint4*>(rp + q * 8);
-        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
-               f3 = unpack_bf16x2(b.w);
-        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
-        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
-      }
-    } else {
-      #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) v[j] += __bfloat162float(rp[j]);
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      v[2 * j] += f.x; v[2 * j + 1] += f.y;
     }
-  } else if (p.epi == kEpiGelu) {
-    // keep the pre-activation for the backward pass, output the activation
-    __nv_bfloat16* ap = p.aux_out + grow * p.ldaux + gcol;
-    if (full) {
+  } else if (EPI == kEpiGelu) {
+    // keep the pre-activation for the backward pass, output the activation of its bf16 rounding
+    uint32_t w[16];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 o;
-        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-        *reinterpret_cast<uint4*>(ap + q * 8) = o;
-      }
-    } else {
-      #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) ap[j] = __float2bfloat16(v[j]);
+    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    st_row(p.aux_out + grow * p.ldaux + gcol, w, wide);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      v[2 * j] = gelu_tanh(f.x); v[2 * j + 1] = gelu_tanh(f.y);
     }
+  } else if (EPI == kEpiGeluGrad) {
+    uint32_t w[16];
+    ld_row(p.aux_in + grow * p.ldaux + gcol, w, wide);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      // the activation is taken of the bf16-rounded pre-activation, as the backward pass sees it
-      float x = __bfloat162float(__float2bfloat16(v[j]));
-      v[j] = gelu_tanh(x);
-    }
-  } else if (p.epi == kEpiGeluGrad) {
-    const __nv_bfloat16* ap = p.aux_in + grow * p.ldaux + gcol;
-    if (full) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 b = *reinterpret_cast<const uint4*>(ap + q * 8);
-        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z),
-               f3 = unpack_bf16x2(b.w);
-        v[q * 8 + 0] *= gelu_tanh_grad(f0.x); v[q * 8 + 1] *= gelu_tanh_grad(f0.y);
-        v[q * 8 + 2] *= gelu_tanh_grad(f1.x); v[q * 8 + 3] *= gelu_tanh_grad(f1.y);
-        v[q * 8 + 4] *= gelu_tanh_grad(f2.x); v[q * 8 + 5] *= gelu_tanh_grad(f2.y);
-        v[q * 8 + 6] *= gelu_tanh_grad(f3.x); v[q * 8 + 7] *= gelu_tanh_grad(f3.y);
-      }
-    } else {
-      #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) v[j] *= gelu_tanh_grad(__bfloat162float(ap[j]));
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      v[2 * j] *= gelu_tanh_grad(f.x); v[2 * j + 1] *= gelu_tanh_grad(f.y);
     }
   }
-
-  if (p.out_fp32) {
+  if (OUT_FP32) {
     float* cp = reinterpret_cast<float*>(p.C) + grow * p.ldc + gcol;
-    if (p.epi == kEpiAtomicAdd) {
-      if (full) {
+    if (EPI == kEpiAtomicAdd) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4),
-                       "f"(v[q * 4 + 0]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
-                       : "memory");
-        }
-      } else {
-        #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) atomicAdd(cp + j, v[j]);
-      }
-    } else if (p.epi == kEpiAccumulate) {
-      if (full) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float4 o = *reinterpret_cast<float4*>(cp + q * 4);
-          o.x += v[q * 4 + 0]; o.y += v[q * 4 + 1]; o.z += v[q * 4 + 2]; o.w += v[q * 4 + 3];
-          *reinterpret_cast<float4*>(cp + q * 4) = o;
-        }
-      } else {
-        #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) cp[j] += v[j];
+      for (int q = 0; q < 8; ++q) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4), "f"(v[q * 4 + 0]),
+                     "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                     : "memory");
       }
     } else {
-      if (full) {
+      uint32_t w[32];
+      if (EPI == kEpiAccumulate) {
+        ld_row(cp, w, wide);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          *reinterpret_cast<float4*>(cp + q * 4) =
-              make_float4(v[q * 4 + 0], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-        }
+        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) + v[j]);
       } else {
-        #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) cp[j] = v[j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
       }
+      st_row(cp, w, wide);
     }
   } else {
-    __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + gcol;
-    if (full) {
+    uint32_t w[16];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 o;
-        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-        *reinterpret_cast<uint4*>(cp + q * 8) = o;
-      }
+    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    st_row(reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + gcol, w, wide);
+  }
+}
+
+// The same for a block at the right edge (fewer than 32 columns exist) or for a combination of
+// kind and output type that has no instantiation above: one element at a time, loop kept
+// rolled so that this seldom-run code stays small.
+static __device__ __noinline__ void epilogue_row_edge(int epi, int out_fp32, void* C, long long ldc,
+                                               const __nv_bfloat16* residual, long long ldr,
+                                               __nv_bfloat16* aux_out, const __nv_bfloat16* aux_in,
+                                               long long ldaux, const uint32_t* r, long long grow,
+                                               int gcol, int ncols, const float* sbias) {
+#pragma unroll 1
+  for (int j = 0; j < ncols; ++j) {
+    float v = __uint_as_float(r[j]);
+    if (sbias != nullptr) v += sbias[j];
+    const long long col = gcol + j;
+    if (epi == kEpiResidual) {
+      v += __bfloat162float(residual[grow * ldr + col]);
+    } else if (epi == kEpiGelu) {
+      const __nv_bfloat16 pre = __float2bfloat16(v);
+      aux_out[grow * ldaux + col] = pre;
+      v = gelu_tanh(__bfloat162float(pre));
+    } else if (epi == kEpiGeluGrad) {
+      v *= gelu_tanh_grad(__bfloat162float(aux_in[grow * ldaux + col]));
+    }
+    if (out_fp32) {
+      float* cp = reinterpret_cast<float*>(C) + grow * ldc + col;
+      if (epi == kEpiAtomicAdd) atomicAdd(cp, v);
+      else if (epi == kEpiAccumulate) *cp += v;
+      else *cp = v;
     } else {
-      #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) cp[j] = __float2bfloat16(v[j]);
+      reinterpret_cast<__nv_bfloat16*>(C)[grow * ldc + col] = __float2bfloat16(v);
     }
   }
 }
 
-
-// Each epilogue warp copies the bias of the 128 columns it will drain into its own 128-float
-// slice of shared memory (lane l takes columns 4l..4l+3), so that the per-chunk epilogue reads
-// it with broadcast loads instead of waiting on global memory. Only a warp-level sync is needed.
-__device__ __forceinline__ void stage_bias(const KernelParams& p, float* my_sbias, int gcol0, int lane) {
-  if (p.bias == nullptr) return;
-  __syncwarp();
+// Epilogue of the four 32-column blocks a warp owns in one tile: r[c] holds block c of the row
+// `grow` (one row per lane), gcol0 is the first column of block 0, sbias the warp's staged bias
+// (128 floats, zero past N) or null.
+template <int EPI, bool OUT_FP32>
+__device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uint32_t (&r)[4][32],
+                                                long long grow, int gcol0, const float* sbias) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int c = gcol0 + lane * 4 + j;
-    my_sbias[lane * 4 + j] = c < p.N ? __bfloat162float(p.bias[c]) : 0.f;
+  for (int c = 0; c < 4; ++c) {
+    const int gcol = gcol0 + c * 32;
+    if (gcol + 32 <= p.N) {
+      epilogue_row<EPI, OUT_FP32>(p, r[c], grow, gcol, sbias != nullptr ? sbias + c * 32 : nullptr);
+    } else if (gcol < p.N) {
+      uint32_t tmp[32];  // addressable copy for the rolled loop
+#pragma unroll
+      for (int j = 0; j < 32; ++j) tmp[j] = r[c][j];
+      epilogue_row_edge(p.epi, p.out_fp32, p.C, p.ldc, p.residual, p.ldr, p.aux_out, p.aux_in, p.ldaux,
+                        tmp, grow, gcol, p.N - gcol, sbias != nullptr ? sbias + c * 32 : nullptr);
+    }
   }
+}
+
+__device__ __forceinline__ void epilogue_tile(const KernelParams& p, const uint32_t (&r)[4][32],
+                                              long long grow, int gcol0, const float* sbias) {
+  if (grow >= p.M) return;
+  if (p.out_fp32) {
+    if (p.epi == kEpiAtomicAdd) return epilogue_blocks<kEpiAtomicAdd, true>(p, r, grow, gcol0, sbias);
+    if (p.epi == kEpiAccumulate) return epilogue_blocks<kEpiAccumulate, true>(p, r, grow, gcol0, sbias);
+    if (p.epi == kEpiNone) return epilogue_blocks<kEpiNone, true>(p, r, grow, gcol0, sbias);
+  } else {
+    if (p.epi == kEpiNone) return epilogue_blocks<kEpiNone, false>(p, r, grow, gcol0, sbias);
+    if (p.epi == kEpiResidual) return epilogue_blocks<kEpiResidual, false>(p, r, grow, gcol0, sbias);
+    if (p.epi == kEpiGelu) return epilogue_blocks<kEpiGelu, false>(p, r, grow, gcol0, sbias);
+    if (p.epi == kEpiGeluGrad) return epilogue_blocks<kEpiGeluGrad, false>(p, r, grow, gcol0, sbias);
+  }
+  // remaining combinations (e.g. residual with an fp32 output): element by element
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int gcol = gcol0 + c * 32;
+    if (gcol < p.N) {
+      uint32_t tmp[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) tmp[j] = r[c][j];
+      epilogue_row_edge(p.epi, p.out_fp32, p.C, p.ldc, p.residual, p.ldr, p.aux_out, p.aux_in, p.ldaux,
+                        tmp, grow, gcol, min(32, p.N - gcol), sbias != nullptr ? sbias + c * 32 : nullptr);
+    }
+  }
+}
+
+// Each epilogue warp copies the bias of the 128 columns it will drain into its own slice of
+// shared memory (lane l takes columns 4l..4l+3, zero past N), so that the row epilogue reads it
+// with broadcast loads. Only warp-level synchronisation is needed. Returns the slice, or null
+// when the GEMM has no bias.
+__device__ __forceinline__ const float* stage_bias(const KernelParams& p, float* my_sbias, int gcol0,
+                                                   int lane) {
+  if (p.bias == nullptr) return nullptr;
+  __syncwarp();  // the previous tile's reads are done
+  const int c = gcol0 + lane * 4;
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c + 4 <= p.N) {
+    b = load_bf16x4(p.bias + c);
+  } else {
+    if (c + 0 < p.N) b.x = __bfloat162float(p.bias[c + 0]);
+    if (c + 1 < p.N) b.y = __bfloat162float(p.bias[c + 1]);
+    if (c + 2 < p.N) b.z = __bfloat162float(p.bias[c + 2]);
+  }
+  *reinterpret_cast<float4*>(my_sbias + lane * 4) = b;
   __syncwarp();
+  return my_sbias;
 }
 
 inline KernelParams make_kernel_params(const GemmArgs& g) {
@@ -185,6 +273,13 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   p.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in);
   p.ldaux = g.ldaux;
   p.status = g.status;
+  {
+    // 32-byte vectors need 32-byte aligned bases and pitches (bf16: 16 elements, fp32: 8)
+    auto a32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+    const long long cmul = g.out_fp32 ? 8 : 16;
+    p.wide = a32(g.C) && (g.ldc % cmul) == 0 && a32(g.residual) && (g.ldr % 16) == 0 && a32(g.aux_out) &&
+             a32(g.aux_in) && (g.ldaux % 16) == 0;
+  }
   return p;
 }
 

@@ -23,6 +23,9 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "gemm.h"
+
+#include "gemm_trace.cuh"
+
 #include "gemm_epilogue.cuh"
 
 namespace z2h {
@@ -39,10 +42,12 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * 128 * 4;
+constexpr int SMEM_BYTES =
+    1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * gemm_detail::kEpiBiasFloats * 4;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
 using gemm_detail::KernelParams;
-using gemm_detail::epilogue_chunk;
+
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -59,10 +64,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* sbias_all = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);
+  float* epi_bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);  // 128 floats per epilogue warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef Z2H_GEMM_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 64) g_epi_n = 0;
+#endif
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -99,6 +107,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      Z2H_TRACE_DECL(0)
+      Z2H_TRACE();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mt = tile % tiles_m;
         const int rest = tile / tiles_m;
@@ -112,6 +122,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             ok = false;
             break;
           }
+          Z2H_TRACE();
           mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
@@ -156,6 +167,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      Z2H_TRACE_DECL(1)
+      Z2H_TRACE();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         const int rest = tile / tiles_m;
         const int ks = rest / tiles_n;
@@ -176,6 +189,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
+          Z2H_TRACE();
           const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
 #pragma unroll
@@ -185,6 +199,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             tc_mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
+          Z2H_TRACE();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -197,9 +212,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------ epilogue (8 warps) ------------------------------
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
-    const int row_in_tile = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
+    Z2H_TRACE_DECL(2)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int mt = tile % tiles_m;
       const int rest = tile / tiles_m;
@@ -209,39 +224,33 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const bool empty_split = kb0 >= num_kb_total;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      // bias of this warp's 128 columns, staged before the wait for the accumulator
+      const int gcol0 = nt * BN + half * 128;
+      const float* sbias = gemm_detail::stage_bias(p, epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats, gcol0, lane);
       if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const long long grow = (long long)mt * BM + row_in_tile;
+      if (warp == 2 && lane == 0) Z2H_TRACE();
+      const long long row_base = (long long)mt * BM + quarter * 32;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      // this warp drains 4 of the 8 column chunks; the next chunk's TMEM load is in flight while
-      // the current one goes through the epilogue
+      // this warp drains 4 of the 8 column blocks of its 32 rows
       const int c0 = half * 4;
-      const int gcol0 = nt * BN + c0 * 32;
-      float* my_sbias = sbias_all + (warp - 2) * 128;
-      gemm_detail::stage_bias(p, my_sbias, gcol0, lane);
-      uint32_t r[2][32];
-      tmem_ld_32x32b_x32(taddr + c0 * 32, r[0]);
+      // All four TMEM loads are issued back to back and awaited once: a load issued while the
+      // tensor core has MMAs queued completes only after ~1000 cycles, and paying that once
+      // per tile instead of once per block is what keeps the epilogue shorter than the main
+      // loop. The accumulator is handed back as soon as it is in registers.
+      uint32_t r[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld_32x32b_x32(taddr + (c0 + c + 1) * 32, r[(c + 1) & 1]);
-        if (c == 3) {
-          // the accumulator part this warp owns is in registers now: hand it back
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        }
-        const int gcol = gcol0 + c * 32;
-        if (grow < p.M && gcol < p.N && !empty_split) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[c & 1][j]);
-          epilogue_chunk(p, v, grow, gcol, p.bias != nullptr ? my_sbias + c * 32 : nullptr);
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + (c0 + c) * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (warp == 2 && lane == 0) Z2H_TRACE();
+      if (!empty_split) gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias);
+      if (warp == 2 && lane == 0) Z2H_TRACE();
     }
   }
 
@@ -306,6 +315,10 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   if (g.epi == kEpiResidual && (g.residual == nullptr || (g.ldr % 8))) return 1;
   if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
+  if (reinterpret_cast<uintptr_t>(g.bias) & 7) return 1;
+  if ((reinterpret_cast<uintptr_t>(g.residual) & 15) || (reinterpret_cast<uintptr_t>(g.aux_out) & 15) ||
+      (reinterpret_cast<uintptr_t>(g.aux_in) & 15))
+    return 1;
   {
     const long long tiles256 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * (g.split_k < 1 ? 1 : g.split_k);
     const bool pair = g_algo == 1 ? g.M >= 256 : (g_algo == 2 && g.M >= 256 && tiles256 >= 74);
@@ -319,6 +332,11 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace z2h
 
+#ifdef Z2H_GEMM_TRACE
+extern "C" int z2h_gemm_trace_read(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
+}
+#endif
 extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }
 extern "C" int z2h_gemm_get_algo() { return z2h::gemm_get_algo(); }
 extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,

@@ -16,13 +16,13 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "gemm.h"
+#include "gemm_trace.cuh"
 #include "gemm_epilogue.cuh"
 
 namespace z2h {
 namespace {
 
 using gemm_detail::KernelParams;
-using gemm_detail::epilogue_chunk;
 
 constexpr int TM = 256;        // tile rows per CTA pair
 constexpr int HM = 128;        // tile rows per CTA
@@ -36,7 +36,9 @@ constexpr int B_STAGE_BYTES = HN * BK * 2;  // 16 KiB
 constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * 128 * 4;
+constexpr int SMEM_BYTES =
+    STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * gemm_detail::kEpiBiasFloats * 4;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -51,7 +53,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* sbias_all = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);
+  float* epi_bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);  // 128 floats per epilogue warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -99,6 +101,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      Z2H_TRACE_DECL(0)
+      Z2H_TRACE();
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
         const int mt = tile % tiles_m;
         const int rest = tile / tiles_m;
@@ -113,6 +117,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             ok = false;
             break;
           }
+          Z2H_TRACE();
           // the leader's barrier counts the bytes of both CTAs
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
@@ -155,6 +160,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      Z2H_TRACE_DECL(1)
+      Z2H_TRACE();
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
         const int rest = tile / tiles_m;
         const int ks = rest / tiles_n;
@@ -174,6 +181,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             break;
           }
           tc_fence_after();
+          Z2H_TRACE();
           const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
           const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
 #pragma unroll
@@ -181,6 +189,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tc_mma_f16_ss_2cta(d_tmem, desc_advance(adesc0, k * a_kstep), desc_advance(bdesc0, k * b_kstep),
                                idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           tc_commit_2cta(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          Z2H_TRACE();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -193,9 +202,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // ------------------------------ epilogue (8 warps per CTA) ------------------------------
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
-    const int row_in_half = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
+    Z2H_TRACE_DECL(2)
     for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
       const int mt = tile % tiles_m;
       const int rest = tile / tiles_m;
@@ -204,39 +213,33 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const bool empty_split = ks * kb_per_split >= num_kb_total;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      // bias of this warp's 128 columns, staged before the wait for the accumulator
+      const int gcol0 = nt * BN + half * 128;
+      const float* sbias = gemm_detail::stage_bias(p, epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats, gcol0, lane);
       if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const long long grow = (long long)mt * TM + (long long)rank * HM + row_in_half;
+      if (warp == 2 && lane == 0) Z2H_TRACE();
+      const long long row_base = (long long)mt * TM + (long long)rank * HM + quarter * 32;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      // this warp drains 4 of the 8 column chunks; the next chunk's TMEM load is in flight while
-      // the current one goes through the epilogue
+      // this warp drains 4 of the 8 column blocks of its 32 rows
       const int c0 = half * 4;
-      const int gcol0 = nt * BN + c0 * 32;
-      float* my_sbias = sbias_all + (warp - 2) * 128;
-      gemm_detail::stage_bias(p, my_sbias, gcol0, lane);
-      uint32_t r[2][32];
-      tmem_ld_32x32b_x32(taddr + c0 * 32, r[0]);
+      // All four TMEM loads are issued back to back and awaited once: a load issued while the
+      // tensor core has MMAs queued completes only after ~1000 cycles, and paying that once
+      // per tile instead of once per block is what keeps the epilogue shorter than the main
+      // loop. The accumulator is handed back as soon as it is in registers.
+      uint32_t r[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld_32x32b_x32(taddr + (c0 + c + 1) * 32, r[(c + 1) & 1]);
-        if (c == 3) {
-          // the accumulator part this warp owns is in registers now: hand it back
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);
-        }
-        const int gcol = gcol0 + c * 32;
-        if (grow < p.M && gcol < p.N && !empty_split) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[c & 1][j]);
-          epilogue_chunk(p, v, grow, gcol, p.bias != nullptr ? my_sbias + c * 32 : nullptr);
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + (c0 + c) * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);
+      if (warp == 2 && lane == 0) Z2H_TRACE();
+      if (!empty_split) gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias);
+      if (warp == 2 && lane == 0) Z2H_TRACE();
     }
   }
 
@@ -307,3 +310,9 @@ int gemm_bf16_pair(const GemmArgs& g, cudaStream_t stream) {
 }
 
 }  // namespace z2h
+
+#ifdef Z2H_GEMM_TRACE
+extern "C" int z2h_gemm_trace_read_pair(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
+}
+#endif

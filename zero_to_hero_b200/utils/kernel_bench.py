@@ -46,7 +46,10 @@ def time_kernel(fn, iters: int, warmup: int = 3, flush: bool = True) -> float:
     times = []
     for _ in range(iters):
         if flush:
-            flush_l2()
+            # three passes keep the GPU busy for ~130 us, so the host has queued the events and the
+            # launch before the GPU reaches them and no launch latency falls between the events
+            for _ in range(3):
+                flush_l2()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         fn()
@@ -183,7 +186,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch library op")
+    ap.add_argument("--gemm-algo", dest="gemm_algo", type=int, default=-1,
+                    help="0: one-CTA kernel, 1: CTA-pair kernel wherever it applies, 2: automatic")
     a = ap.parse_args()
+    if a.gemm_algo >= 0:
+        G.set_algo(a.gemm_algo)
     if a.split_k > 1:
         a.fp32_out = True
     dev = torch.device("cuda")
