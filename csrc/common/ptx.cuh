@@ -240,6 +240,14 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
       : "memory");
 }
 
+// 1-D bulk copy shared -> global as part of the current bulk group (commit with
+// tma_store_commit, wait with tma_store_wait_read / tma_store_wait). Same 16-byte rules.
+__device__ __forceinline__ void bulk_store_1d(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread i <-> lane i of
 // the warp's TMEM lane quarter).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -25,7 +25,8 @@ struct GemmArgs {
   const void* B; int b_mn; long long ldb;
   void* C; long long ldc; int out_fp32;
   int M, N, K;
-  int epi; int split_k;
+  int epi;
+  int split_k;            // > 1: K cut into slices; <= 0 with kEpiAtomicAdd: stream-K (one run of k-blocks per SM)
   const void* bias;       // bf16 [N] or null
   const void* residual;   // bf16 [M, ldr]
   long long ldr;

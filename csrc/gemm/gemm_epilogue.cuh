@@ -20,7 +20,60 @@ struct KernelParams {
   const __nv_bfloat16* aux_in;
   long long ldaux;
   int* status;
-  int wide;  // every row segment the epilogue touches is 32-byte aligned
+  int wide;      // every row segment the epilogue touches is 32-byte aligned
+  int stream_k;  // work is cut into equal runs of k-blocks instead of whole tiles (atomic-add epilogue only)
+};
+
+// One unit of work of a CTA (or CTA pair): k-blocks [kb0, kb1) of output tile (mt, nt).
+struct Segment {
+  int mt, nt, kb0, kb1;
+};
+
+// Static work distribution, the same sequence for every role of a worker (a CTA or CTA pair).
+//   tiles / split-K: items (tile, k-slice) are dealt round-robin, M fastest, so the workers that
+//     run at the same time share one B panel out of L2;
+//   stream-K: the tiles x k-blocks units are cut into `workers` equal contiguous runs, a run is
+//     walked tile by tile, and every piece is added to the output atomically. No worker idles in
+//     a last partial wave, which is what the weight-gradient GEMMs (few tiles, very long K) need.
+struct TileScheduler {
+  int tiles_m, tiles_n, num_kb, kb_per_split, total_items, item, stride, stream_k;
+  long long u, u_end;
+  __device__ TileScheduler(const KernelParams& p, int bm, int bn, int bk, int worker, int workers) {
+    tiles_m = (p.M + bm - 1) / bm;
+    tiles_n = (p.N + bn - 1) / bn;
+    num_kb = (p.K + bk - 1) / bk;
+    stream_k = p.stream_k;
+    kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
+    total_items = tiles_m * tiles_n * p.split_k;
+    item = worker;
+    stride = workers;
+    const long long total = (long long)tiles_m * tiles_n * num_kb;
+    const long long per = (total + workers - 1) / workers;
+    u = per * worker;
+    u_end = u + per < total ? u + per : total;
+  }
+  __device__ bool next(Segment& s) {
+    if (stream_k) {
+      if (u >= u_end) return false;
+      const long long tile = u / num_kb;
+      s.kb0 = (int)(u - tile * num_kb);
+      const long long left = u_end - u;
+      s.kb1 = left < (long long)(num_kb - s.kb0) ? s.kb0 + (int)left : num_kb;
+      s.mt = (int)(tile % tiles_m);
+      s.nt = (int)(tile / tiles_m);
+      u += s.kb1 - s.kb0;
+      return true;
+    }
+    if (item >= total_items) return false;
+    s.mt = item % tiles_m;
+    const int rest = item / tiles_m;
+    s.nt = rest % tiles_n;
+    const int ks = rest / tiles_n;
+    s.kb0 = ks * kb_per_split;
+    s.kb1 = min(num_kb, s.kb0 + kb_per_split);  // may be empty for the last slices
+    item += stride;
+    return true;
+  }
 };
 
 __device__ __forceinline__ float4 load_bf16x4(const __nv_bfloat16* ptr) {
@@ -263,6 +316,7 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   KernelParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.split_k = g.split_k < 1 ? 1 : g.split_k;
+  p.stream_k = (g.split_k <= 0 && g.epi == kEpiAtomicAdd) ? 1 : 0;
   p.epi = g.epi;
   p.out_fp32 = g.out_fp32;
   p.C = g.C; p.ldc = g.ldc;

@@ -72,11 +72,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   if (blockIdx.x == 0 && threadIdx.x == 64) g_epi_n = 0;
 #endif
 
-  const int tiles_m = (p.M + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_kb_total = (p.K + BK - 1) / BK;
-  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;
-  const int total_tiles = tiles_m * tiles_n * p.split_k;
+  // every role walks the same sequence of work segments
+  gemm_detail::TileScheduler sched(p, BM, BN, BK, blockIdx.x, gridDim.x);
+  gemm_detail::Segment sg;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -109,13 +107,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       bool ok = true;
       Z2H_TRACE_DECL(0)
       Z2H_TRACE();
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % tiles_m;
-        const int rest = tile / tiles_m;
-        const int nt = rest % tiles_n;
-        const int ks = rest / tiles_n;
-        const int kb0 = ks * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+      while (ok && sched.next(sg)) {
+        const int mt = sg.mt, nt = sg.nt, kb0 = sg.kb0, kb1 = sg.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
                                  kTimeoutEmpty)) {
@@ -169,11 +162,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       bool ok = true;
       Z2H_TRACE_DECL(1)
       Z2H_TRACE();
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-        const int rest = tile / tiles_m;
-        const int ks = rest / tiles_n;
-        const int kb0 = ks * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+      for (; ok && sched.next(sg); ++it) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status,
@@ -215,13 +205,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int it = 0;
     bool ok = true;
     Z2H_TRACE_DECL(2)
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const int mt = tile % tiles_m;
-      const int rest = tile / tiles_m;
-      const int nt = rest % tiles_n;
-      const int ks = rest / tiles_n;
-      const int kb0 = ks * kb_per_split;
-      const bool empty_split = kb0 >= num_kb_total;
+    for (; ok && sched.next(sg); ++it) {
+      const int mt = sg.mt, nt = sg.nt;
+      const bool empty_split = sg.kb0 >= sg.kb1;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // bias of this warp's 128 columns, staged before the wait for the accumulator
@@ -289,8 +275,9 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     attr_set = true;
   }
-  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * p.split_k;
-  int grid = tiles < num_sms ? tiles : num_sms;
+  const long long tiles = (long long)((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) *
+                          (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);
+  int grid = tiles < num_sms ? (int)tiles : num_sms;
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   if (grid < 1) return 0;
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
@@ -320,8 +307,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(g.aux_in) & 15))
     return 1;
   {
+    const bool stream_k = g.split_k <= 0 && g.epi == kEpiAtomicAdd;  // fills every SM whatever the tile count
     const long long tiles256 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * (g.split_k < 1 ? 1 : g.split_k);
-    const bool pair = g_algo == 1 ? g.M >= 256 : (g_algo == 2 && g.M >= 256 && tiles256 >= 74);
+    const bool pair = g_algo == 1 ? g.M >= 256 : (g_algo == 2 && g.M >= 256 && (stream_k || tiles256 >= 74));
     if (pair) return gemm_bf16_pair(g, stream);
   }
   if (g.a_mn == 0 && g.b_mn == 0) return launch<0, 0>(g, stream);

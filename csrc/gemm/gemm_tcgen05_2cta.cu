@@ -62,11 +62,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int num_pairs = gridDim.x >> 1;
   const bool aligned = (smem_u32(smem_raw) & 1023u) == 0;
 
-  const int tiles_m = (p.M + TM - 1) / TM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_kb_total = (p.K + BK - 1) / BK;
-  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;
-  const int total_tiles = aligned ? tiles_m * tiles_n * p.split_k : 0;
+  // every role of both CTAs walks the same sequence of work segments (none if misaligned)
+  gemm_detail::TileScheduler sched(p, TM, BN, BK, aligned ? pair : 0, aligned ? num_pairs : 1);
+  if (!aligned) sched.total_items = 0, sched.u_end = sched.u;
+  gemm_detail::Segment sg;
   if (!aligned && threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
 
   if (threadIdx.x == 0) {
@@ -103,13 +102,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       Z2H_TRACE_DECL(0)
       Z2H_TRACE();
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
-        const int mt = tile % tiles_m;
-        const int rest = tile / tiles_m;
-        const int nt = rest % tiles_n;
-        const int ks = rest / tiles_n;
-        const int kb0 = ks * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+      while (ok && sched.next(sg)) {
+        const int mt = sg.mt, nt = sg.nt, kb0 = sg.kb0, kb1 = sg.kb1;
         const int m0 = mt * TM + (int)rank * HM;
         const int n0 = nt * BN + (int)rank * HN;
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -162,11 +156,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       Z2H_TRACE_DECL(1)
       Z2H_TRACE();
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
-        const int rest = tile / tiles_m;
-        const int ks = rest / tiles_n;
-        const int kb0 = ks * kb_per_split;
-        const int kb1 = min(num_kb_total, kb0 + kb_per_split);
+      for (; ok && sched.next(sg); ++it) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, kTimeoutTmemEmpty)) {
@@ -205,12 +196,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int it = 0;
     bool ok = true;
     Z2H_TRACE_DECL(2)
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
-      const int mt = tile % tiles_m;
-      const int rest = tile / tiles_m;
-      const int nt = rest % tiles_n;
-      const int ks = rest / tiles_n;
-      const bool empty_split = ks * kb_per_split >= num_kb_total;
+    for (; ok && sched.next(sg); ++it) {
+      const int mt = sg.mt, nt = sg.nt;
+      const bool empty_split = sg.kb0 >= sg.kb1;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // bias of this warp's 128 columns, staged before the wait for the accumulator
@@ -280,10 +268,11 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     attr_set = true;
   }
-  const int tiles = ((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) * p.split_k;
+  const long long tiles = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) *
+                          (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);
   int pairs = num_sms / 2;
   if (g.max_ctas > 0 && pairs > g.max_ctas / 2) pairs = g.max_ctas / 2 > 0 ? g.max_ctas / 2 : 1;
-  if (tiles < pairs) pairs = tiles;
+  if (tiles < pairs) pairs = (int)tiles;
   if (pairs < 1) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);

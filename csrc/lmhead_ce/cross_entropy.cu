@@ -1,11 +1,13 @@
 // Softmax cross-entropy over bf16 logits, fused with its own backward.
 //
-// One CTA per row. Pass 1 streams the row once (16-byte loads) keeping a running
-// (max, sum-exp) per thread, folds them across the CTA, and writes the row loss
-// lse - logit[target]. Pass 2 re-reads the row, which is still in L2, and overwrites it in
-// place with dlogits = (softmax - onehot) * grad_scale, so the lm_head data- and
-// weight-gradient GEMMs can consume the same buffer. Columns >= V_real (vocabulary padding)
-// never enter the softmax and get a zero gradient.
+// One CTA per row. Rows of up to 112 KiB are copied into shared memory by one bulk copy
+// (cp.async.bulk + mbarrier), the maximum, the sum of exponentials and the gradient are taken
+// from there, and one bulk copy writes the row back: the row is read from memory exactly once,
+// written once, and two CTAs per SM overlap one row's copies with the other's arithmetic. The row loss is
+// lse - logit[target]; the row is overwritten in place with dlogits = (softmax - onehot) *
+// grad_scale, so the lm_head data- and weight-gradient GEMMs can consume the same buffer.
+// Columns >= V_real (vocabulary padding) never enter the softmax and get a zero gradient.
+// Longer rows take a streaming kernel with a running (max, sum-exp) pair and a second read.
 //
 // Semantics: F.cross_entropy(logits.view(B*T, V), Y.view(B*T)) as in nn/gpt2/modules.py:115-117
 // (mean over rows is applied through grad_scale and by the caller for the loss); the fused
@@ -27,6 +29,137 @@ __device__ __forceinline__ void online_add(float& m, float& s, float x) {
   }
 }
 
+constexpr int kRowThreads = 512;
+constexpr int kRowMaxBytes = 112 * 1024;  // two CTAs of this size share an SM
+constexpr float kLog2e = 1.4426950408889634f;
+
+// blockDim.x == kRowThreads; returns the maximum (IS_MAX) or the sum of v over the CTA
+template <bool IS_MAX>
+__device__ __forceinline__ float cta_reduce(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float t = __shfl_xor_sync(0xffffffffu, v, o);
+    v = IS_MAX ? fmaxf(v, t) : v + t;
+  }
+  __syncthreads();  // sh may still be read from the previous reduction
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = (threadIdx.x & 31) < kRowThreads / 32 ? sh[threadIdx.x & 31] : (IS_MAX ? -INFINITY : 0.f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float t = __shfl_xor_sync(0xffffffffu, v, o);
+    v = IS_MAX ? fmaxf(v, t) : v + t;
+  }
+  return v;
+}
+
+// One CTA per row, the row held in shared memory: one bulk copy brings it in, three passes over
+// shared memory take the maximum, the sum of exponentials and the gradient (written in place),
+// one bulk copy writes it back. Two CTAs fit on an SM, so one row's copies overlap the other
+// row's arithmetic and ~200 KB per SM are in flight.
+template <typename IdxT>
+__global__ void __launch_bounds__(kRowThreads)
+ce_row_in_smem_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ targets,
+                      float* __restrict__ losses, int V_real, int V_pad, long long ld, float grad_scale,
+                      int write_grad, int ignore_index, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float sh[32];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + (long long)row * ld;
+  const uint32_t row_bytes = (uint32_t)V_pad * 2;  // a multiple of 16
+  const int nvec = V_pad / 8;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+    mbar_arrive_expect_tx(&bar, row_bytes);
+    bulk_load_1d(smem, lr, row_bytes, &bar);
+  }
+  __syncthreads();
+  const long long tgt = (long long)targets[row];
+  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V_real;
+  if (!mbar_wait_bounded(&bar, 0, &abort_flag, status, kTimeoutFull)) return;
+  const uint4* sv = reinterpret_cast<const uint4*>(smem);
+  const int vlast = V_real / 8;  // first vector that may contain padding columns
+  // ---- maximum (padding columns are skipped)
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
+    const uint4 u = sv[v];
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+    if (v < vlast) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        m = max3(m, f.x, f.y);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        const int c = v * 8 + 2 * j;
+        if (c < V_real) m = fmaxf(m, f.x);
+        if (c + 1 < V_real) m = fmaxf(m, f.y);
+      }
+    }
+  }
+  m = cta_reduce<true>(m, sh);
+  const float m2 = m * kLog2e;
+  // ---- sum of exponentials
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
+    const uint4 u = sv[v];
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      const float e0 = ex2_fast(fmaf(f.x, kLog2e, -m2)), e1 = ex2_fast(fmaf(f.y, kLog2e, -m2));
+      if (v < vlast) {
+        s += e0 + e1;
+      } else {
+        const int c = v * 8 + 2 * j;
+        if (c < V_real) s += e0;
+        if (c + 1 < V_real) s += e1;
+      }
+    }
+  }
+  s = cta_reduce<false>(s, sh);
+  const float lse = m + __logf(s);
+  if (threadIdx.x == 0 && losses != nullptr)
+    losses[row] = ignored ? 0.f : lse - __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(smem)[tgt]);
+  if (!write_grad) return;
+  __syncthreads();  // the target logit has been read before anybody overwrites the row
+  // ---- gradient, in place
+  const float gs = ignored ? 0.f : grad_scale;
+  const float lse2 = lse * kLog2e;
+  uint4* sw = reinterpret_cast<uint4*>(smem);
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
+    uint4 u = sw[v];
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      const int c = v * 8 + 2 * j;
+      float g0 = (ex2_fast(fmaf(f.x, kLog2e, -lse2)) - (c == tgt ? 1.f : 0.f)) * gs;
+      float g1 = (ex2_fast(fmaf(f.y, kLog2e, -lse2)) - (c + 1 == tgt ? 1.f : 0.f)) * gs;
+      if (v >= vlast) {
+        if (c >= V_real) g0 = 0.f;
+        if (c + 1 >= V_real) g1 = 0.f;
+      }
+      w[j] = pack_bf16x2(g0, g1);
+    }
+    sw[v] = u;
+  }
+  fence_proxy_async();  // make the generic-proxy writes visible to the bulk copy
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bulk_store_1d(lr, smem, row_bytes);
+    tma_store_commit();
+    tma_store_wait_read<0>();  // shared memory must stay alive until the copy has read it
+  }
+}
+
 template <typename IdxT>
 __global__ void __launch_bounds__(kThreads)
 ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ targets,
@@ -37,6 +170,10 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ t
   const int row = blockIdx.x;
   __nv_bfloat16* lr = logits + (long long)row * ld;
   const int nvec = V_pad / 8;
+  const long long tgt = (long long)targets[row];
+  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V_real;
+  // taken now: the row is overwritten in place further down
+  const float tgt_logit = (threadIdx.x == 0 && !ignored) ? __bfloat162float(lr[tgt]) : 0.f;
   float m = -INFINITY, s = 0.f;
   for (int i = threadIdx.x; i < nvec; i += kThreads) {
     uint4 u = *reinterpret_cast<const uint4*>(lr + i * 8);
@@ -82,10 +219,7 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ t
   }
   __syncthreads();
   const float lse = row_lse;
-  long long tgt = (long long)targets[row];
-  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V_real;
-  if (threadIdx.x == 0 && losses != nullptr)
-    losses[row] = ignored ? 0.f : lse - __bfloat162float(lr[tgt]);
+  if (threadIdx.x == 0 && losses != nullptr) losses[row] = ignored ? 0.f : lse - tgt_logit;
   if (!write_grad) return;
   const float gs = ignored ? 0.f : grad_scale;
   for (int i = threadIdx.x; i < nvec; i += kThreads) {
@@ -132,6 +266,27 @@ int ce_fwd_bwd(void* logits, const void* targets, int idx_is_64, float* losses, 
                cudaStream_t stream) {
   if (M <= 0) return 0;
   if (ld % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15)) return 1;
+  // rows that fit in shared memory twice per SM (the usual case: GPT-2's 50,304 columns are 98 KiB)
+  const size_t row_bytes = (size_t)V_pad * 2;
+  if (V_pad % 8 == 0 && row_bytes <= (size_t)kRowMaxBytes) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(ce_row_in_smem_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kRowMaxBytes);
+      cudaFuncSetAttribute(ce_row_in_smem_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kRowMaxBytes);
+      attr_set = true;
+    }
+    if (idx_is_64)
+      ce_row_in_smem_kernel<long long><<<M, kRowThreads, row_bytes, stream>>>(
+          (__nv_bfloat16*)logits, (const long long*)targets, losses, V_real, V_pad, ld, grad_scale,
+          write_grad, ignore_index, nullptr);
+    else
+      ce_row_in_smem_kernel<int><<<M, kRowThreads, row_bytes, stream>>>(
+          (__nv_bfloat16*)logits, (const int*)targets, losses, V_real, V_pad, ld, grad_scale, write_grad,
+          ignore_index, nullptr);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+  }
   if (idx_is_64)
     ce_fwd_bwd_kernel<long long><<<M, kThreads, 0, stream>>>((__nv_bfloat16*)logits,
                                                             (const long long*)targets, losses, V_real,

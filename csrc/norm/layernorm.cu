@@ -101,7 +101,7 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 
 // scratch layout: [gridDim.x][2][C] fp32 (dw partials, then db partials)
 template <int NVEC, bool HAS_DB>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, NVEC <= 4 ? 2 : 1)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
@@ -125,14 +125,30 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   for (int row = blockIdx.x * kWarpsPerCta + warp; row < M; row += gridDim.x * kWarpsPerCta) {
     const long long off = (long long)row * C;
     const float mean = mean_in[row], rstd = rstd_in[row];
-    uint4 dyraw[NVEC], xraw[NVEC];
-    float s1 = 0.f, s2 = 0.f;
+    uint4 dyraw[NVEC], xraw[NVEC], rraw[NVEC];
+    // every load of this row is issued before the first use, and the lines of the warp's next
+    // row are requested into L2 meanwhile
+    const int next_row = row + gridDim.x * kWarpsPerCta;
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int c = (i * 32 + lane) * 8;
       if (c < C) {
         dyraw[i] = *reinterpret_cast<const uint4*>(dy + off + c);
         xraw[i] = *reinterpret_cast<const uint4*>(x + off + c);
+        if (dresid != nullptr) rraw[i] = *reinterpret_cast<const uint4*>(dresid + off + c);
+        if (next_row < M && (lane & 7) == 0) {  // one request per 128-byte line
+          const long long noff = (long long)next_row * C + c;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + noff));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x + noff));
+          if (dresid != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(dresid + noff));
+        }
+      }
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
         const uint32_t* dyu = reinterpret_cast<const uint32_t*>(&dyraw[i]);
         const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xraw[i]);
         const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw[i]);
@@ -170,10 +186,13 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
           o[2 * j + 1] = rstd * (d.y * wv.y - s1 - xh1 * s2);
         }
         if (dresid != nullptr) {
-          float r[8];
-          load8(dresid + off + c, r);
+          const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rraw[i]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
+          for (int j = 0; j < 4; ++j) {
+            const float2 r = unpack_bf16x2(ru[j]);
+            o[2 * j] += r.x;
+            o[2 * j + 1] += r.y;
+          }
         }
         store8(dx + off + c, o);
       }

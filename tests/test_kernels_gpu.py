@@ -88,6 +88,29 @@ def test_gemm_deterministic_without_atomics(dev):
     assert torch.equal(o1, o2)
 
 
+@pytest.mark.parametrize("algo", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(768, 768, 4096), (2304, 768, 2048), (300, 520, 1000), (256, 256, 64)])
+def test_gemm_stream_k(dev, algo, M, N, K):
+    """Weight-gradient form (both operands MN-major, fp32 atomic accumulation) under the stream-K
+    schedule: every CTA gets an equal run of k-blocks that may span several output tiles."""
+    from zero_to_hero_b200.ops import gemm as G
+    Kp = (K + 7) // 8 * 8
+    Mp, Np = (M + 7) // 8 * 8, (N + 7) // 8 * 8
+    At = torch.randn(Kp, Mp, device=dev).bfloat16()[:K, :M]  # [K, M], pitch a multiple of 8
+    Bt = torch.randn(Kp, Np, device=dev).bfloat16()[:K, :N]
+    base = At.float().t() @ Bt.float()
+    start = torch.randn(M, Np, device=dev)[:, :N]
+    out = start.clone()
+    prev = G.get_algo()
+    try:
+        G.set_algo(algo)
+        G.gemm(At, Bt, out, a_mn=True, b_mn=True, epi=G.EPI_ATOMIC_ADD, split_k=0)
+    finally:
+        G.set_algo(prev)
+    assert rel_err(out, base + start) < 1e-4
+    status_ok()
+
+
 def test_gemm_rejects_unaligned(dev):
     from zero_to_hero_b200.ops import gemm as G
     A = torch.randn(64, 68, device=dev).bfloat16()[:, :65]  # pitch 68 is not a multiple of 8

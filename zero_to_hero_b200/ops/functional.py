@@ -28,16 +28,15 @@ def _native(t: torch.Tensor) -> bool:
 
 
 def pick_split_k(tiles: int, k_blocks: int, num_sms: int = 148, min_kb: int = 16) -> int:
-    """Split-K factor for a weight-gradient GEMM: fill the SMs while keeping >= min_kb K-blocks
-    per split. Minimises waves / split (ties go to the smaller split)."""
-    best, best_cost = 1, float("inf")
-    for s in range(1, 33):
-        if s > 1 and k_blocks // s < min_kb:
-            break
-        cost = math.ceil(tiles * s / num_sms) / s
-        if cost < best_cost - 1e-9:
-            best, best_cost = s, cost
-    return best
+    """How a weight-gradient GEMM (few output tiles, very long K) should be cut up.
+
+    Returns 1 when the tiles alone fill the SMs for several waves (plain deterministic
+    accumulation), otherwise 0, which selects the stream-K schedule of the kernel: all tile x
+    k-block units are cut into one equal run per SM and partial tiles are added atomically.
+    """
+    if tiles >= 4 * num_sms or k_blocks < 2 * min_kb:
+        return 1
+    return 0
 
 
 def _gemm_ok(*dims: int) -> bool:

@@ -39,6 +39,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
 
     `a` is [M,K] (or [K,M] when `a_mn`), `b` is [N,K] (or [K,N] when `b_mn`); both bf16 with a
     unit inner stride. `out` is bf16 or fp32 [M,N]. See csrc/gemm/gemm.h for the epilogues.
+    `split_k` > 1 cuts K into that many slices; 0 selects the stream-K schedule (one equal run of
+    k-blocks per SM); both need `epi=EPI_ATOMIC_ADD` and an fp32 `out` that already holds the
+    value to add to.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
