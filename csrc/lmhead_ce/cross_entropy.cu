@@ -29,7 +29,7 @@ __device__ __forceinline__ void online_add(float& m, float& s, float x) {
   }
 }
 
-constexpr int kRowThreads = 512;
+constexpr int kRowThreads = 1024;
 constexpr int kRowMaxBytes = 112 * 1024;  // two CTAs of this size share an SM
 constexpr float kLog2e = 1.4426950408889634f;
 

@@ -68,8 +68,13 @@ def main():
         (l0, n0), (l1, n1) = res
         assert abs(l0 - l1) < 1e-3, (step, l0, l1)
         assert abs(n0 - n1) / n1 < 1e-3, (step, n0, n1)
+        # AdamW divides by sqrt(v): where a gradient is almost zero, rounding-level differences
+        # between the two reduction orders move a weight by up to lr per step, so the bound on
+        # the largest difference is loose and the mean difference carries the check
         a, b = engines[0].full_master(), engines[1].full_master()
-        assert rel(a, b) < 1e-3, (step, rel(a, b))
+        assert rel(a, b) < 5e-3, (step, rel(a, b))
+        mean_rel = (a - b).abs().mean().item() / b.abs().mean().item()
+        assert mean_rel < 1e-4, (step, mean_rel)
         # every rank holds the same bf16 working copy after the all-gather
         w = engines[0].p16.float()
         ref = w.clone()
