@@ -28,15 +28,25 @@ def _native(t: torch.Tensor) -> bool:
 
 
 def pick_split_k(tiles: int, k_blocks: int, num_sms: int = 148, min_kb: int = 16) -> int:
-    """How a weight-gradient GEMM (few output tiles, very long K) should be cut up.
+    """Split-K factor for a weight-gradient GEMM (few output tiles, very long K).
 
-    Returns 1 when the tiles alone fill the SMs for several waves (plain deterministic
-    accumulation), otherwise 0, which selects the stream-K schedule of the kernel: all tile x
-    k-block units are cut into one equal run per SM and partial tiles are added atomically.
+    `tiles` counts 128 x 256 output tiles (one per SM); the kernel that runs them works on CTA
+    pairs with 256 x 256 tiles, so the model below uses half as many tiles and half as many
+    workers. Cost of a factor s, in k-blocks of main loop: waves(s) * ceil(k_blocks / s) plus
+    2 * s for the extra atomic accumulation traffic. Returns 1 (plain deterministic accumulation)
+    when the tiles alone fill the machine for several waves.
     """
     if tiles >= 4 * num_sms or k_blocks < 2 * min_kb:
         return 1
-    return 0
+    pair_tiles, workers = max(1, (tiles + 1) // 2), max(1, num_sms // 2)
+    best, best_cost = 1, float("inf")
+    for s in range(1, 17):
+        if s > 1 and k_blocks // s < min_kb:
+            break
+        cost = math.ceil(pair_tiles * s / workers) * math.ceil(k_blocks / s) + 2 * s
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def _gemm_ok(*dims: int) -> bool:

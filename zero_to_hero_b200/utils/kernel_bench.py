@@ -79,7 +79,7 @@ def bench_gemm(a, dev):
     B = torch.randn((K, Nn) if a.b_mn else (Nn, K), device=dev).bfloat16()
     out = torch.zeros(M, Nn, device=dev, dtype=torch.float32 if a.fp32_out else torch.bfloat16)
     kw = {}
-    if a.split_k > 1:
+    if a.split_k > 1 or a.split_k == 0:  # 0: stream-K schedule
         kw = dict(epi=G.EPI_ATOMIC_ADD, split_k=a.split_k)
     ms = time_kernel(lambda: G.gemm(A, B, out, a_mn=a.a_mn, b_mn=a.b_mn, **kw), a.iters, flush=not a.no_flush)
     report(f"gemm M{M} N{Nn} K{K} a_mn{int(a.a_mn)} b_mn{int(a.b_mn)} split{a.split_k}", ms,
@@ -182,7 +182,8 @@ def main():
     ap.add_argument("--a-mn", dest="a_mn", action="store_true")
     ap.add_argument("--b-mn", dest="b_mn", action="store_true")
     ap.add_argument("--fp32-out", dest="fp32_out", action="store_true")
-    ap.add_argument("--split-k", dest="split_k", type=int, default=1)
+    ap.add_argument("--split-k", dest="split_k", type=int, default=1,
+                    help="> 1: split-K slices, 0: stream-K (both with fp32 atomic accumulation)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch library op")
@@ -191,7 +192,7 @@ def main():
     a = ap.parse_args()
     if a.gemm_algo >= 0:
         G.set_algo(a.gemm_algo)
-    if a.split_k > 1:
+    if a.split_k != 1:
         a.fp32_out = True
     dev = torch.device("cuda")
     torch.manual_seed(0)
