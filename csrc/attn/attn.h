@@ -9,4 +9,15 @@ int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* 
 // stats: fp32 scratch of 2 * B * H * roundup(T, 128) elements.
 int flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
               float* dq_accum, float* stats, int B, int T, int H, int* status, cudaStream_t stream);
+// The same with attention-probability dropout (nn/gpt2/modules.py:36 of the reference passes
+// dropout_p to SDPA). drop_p in [0, 1) is quantised to 1/256; the mask is a function of
+// (*seed_ptr, site, b, h, q, k) (csrc/common/dropout.cuh), so forward and backward agree when
+// they are given the same seed and site. drop_p == 0 runs the plain kernels.
+int flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int H, float drop_p,
+                      const unsigned long long* seed_ptr, unsigned int site, int* status,
+                      cudaStream_t stream);
+int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                      float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                      const unsigned long long* seed_ptr, unsigned int site, int* status,
+                      cudaStream_t stream);
 }  // namespace z2h

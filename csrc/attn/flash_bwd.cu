@@ -22,6 +22,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
+#include "../common/dropout.cuh"
 #include <cstdlib>
 
 namespace z2h {
@@ -49,9 +50,16 @@ struct BwdParams {
   int B, T, H, C;
   float scale, scale_log2;
   int* status;
-  int debug;
+  // attention-probability dropout (DROP instantiation only), same stream as the forward kernel
+  float drop_p;
+  const unsigned long long* seed_ptr;
+  uint32_t site;
 };
 
+// DROP: with M the keep mask and s = 1/(1-p), the forward used P~ = P o M * s in P V. Then
+// dV = P~^T dO, dP = (dO V^T) o M * s, and dS = P o (dP - delta) with delta = rowsum(dO o O)
+// unchanged, so the mask enters in two places of the per-element code and nowhere else.
+template <bool DROP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                  const BwdParams p) {
@@ -226,7 +234,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       uint32_t v[32];
       tmem_ld_32x32b_x32(t_lane + DQ_COL + (t & 1) * HD + half * 32, v);
       tmem_ld_wait();
-      if (tq < p.T && !(p.debug & 1)) {
+      if (tq < p.T) {
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 4),
@@ -237,6 +245,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       }
       tc_fence_before();
     };
+    DropoutSpec drop = {};
+    if (DROP) drop = make_dropout_spec(p.seed_ptr, p.site, p.drop_p);
+    const unsigned long long drop_wpr = (unsigned long long)((p.T + 3) / 4);  // mask words per query row
+    const int drop_byte = (j * TS + r) & 3;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int i = j + it;
@@ -252,6 +264,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       }
       tc_fence_after();
       const uint32_t pb = (it & 1) * PT_BYTES;  // which P^T / dS^T buffer this tile uses
+      // mask word of (first query of tile i, this thread's key); one row of words per query
+      const unsigned long long drop_q0 =
+          DROP ? ((unsigned long long)bh * p.T + (unsigned long long)i * TS) * drop_wpr + (unsigned long long)((j * TS + r) >> 2)
+               : 0ull;
       const bool diag = (i == j);
       const int q_valid = p.T - i * TS;  // columns >= q_valid are past the end of the sequence
       const bool fast = !diag && q_valid >= TS;  // no masking anywhere in this tile
@@ -263,7 +279,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64 + 32, sv[1]);
       tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64 + 32, dv[1]);
       tmem_ld_wait();
-      if (!(p.debug & 4))
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
@@ -285,12 +300,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
               if ((diag && c0 + 2 < r) || c0 + 2 >= q_valid) p2 = 0.f;
               if ((diag && c0 + 3 < r) || c0 + 3 >= q_valid) p3 = 0.f;
             }
-            const float d0 = p0 * (__uint_as_float(dv[ch][e4 * 4 + 0]) - D.x);
-            const float d1 = p1 * (__uint_as_float(dv[ch][e4 * 4 + 1]) - D.y);
-            const float d2 = p2 * (__uint_as_float(dv[ch][e4 * 4 + 2]) - D.z);
-            const float d3 = p3 * (__uint_as_float(dv[ch][e4 * 4 + 3]) - D.w);
-            pk[e * 2 + 0] = pack_bf16x2(p0, p1);
-            pk[e * 2 + 1] = pack_bf16x2(p2, p3);
+            float g0 = __uint_as_float(dv[ch][e4 * 4 + 0]), g1 = __uint_as_float(dv[ch][e4 * 4 + 1]);
+            float g2 = __uint_as_float(dv[ch][e4 * 4 + 2]), g3 = __uint_as_float(dv[ch][e4 * 4 + 3]);
+            float pd0 = p0, pd1 = p1, pd2 = p2, pd3 = p3;  // what multiplied V in the forward pass
+            if (DROP) {
+              // this thread's key is fixed; the four queries of this step are consecutive rows
+              const unsigned long long w0 = drop_q0 + (unsigned long long)(half * 64 + ch * 32 + e4 * 4) * drop_wpr;
+              const bool k0 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0), drop_byte, drop.threshold);
+              const bool k1 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0 + drop_wpr), drop_byte, drop.threshold);
+              const bool k2 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0 + 2 * drop_wpr), drop_byte, drop.threshold);
+              const bool k3 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0 + 3 * drop_wpr), drop_byte, drop.threshold);
+              pd0 = k0 ? p0 * drop.scale : 0.f; g0 = k0 ? g0 * drop.scale : 0.f;
+              pd1 = k1 ? p1 * drop.scale : 0.f; g1 = k1 ? g1 * drop.scale : 0.f;
+              pd2 = k2 ? p2 * drop.scale : 0.f; g2 = k2 ? g2 * drop.scale : 0.f;
+              pd3 = k3 ? p3 * drop.scale : 0.f; g3 = k3 ? g3 * drop.scale : 0.f;
+            }
+            const float d0 = p0 * (g0 - D.x);
+            const float d1 = p1 * (g1 - D.y);
+            const float d2 = p2 * (g2 - D.z);
+            const float d3 = p3 * (g3 - D.w);
+            pk[e * 2 + 0] = pack_bf16x2(pd0, pd1);
+            pk[e * 2 + 1] = pack_bf16x2(pd2, pd3);
             dk[e * 2 + 0] = pack_bf16x2(d0, d1);
             dk[e * 2 + 1] = pack_bf16x2(d2, d3);
           }
@@ -437,9 +467,12 @@ __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
 
 }  // namespace
 
-int flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
-              float* dq_accum, float* stats, int B, int T, int H, int* status, cudaStream_t stream) {
+int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                      float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                      const unsigned long long* seed_ptr, unsigned int site, int* status,
+                      cudaStream_t stream) {
   const int C = H * HD;
+  if (!(drop_p >= 0.f) || drop_p >= 1.f) return 1;
   if (B <= 0 || T <= 0) return 0;
   const int Tpad = (T + TS - 1) / TS * TS;
   CUtensorMap tm_qkv, tm_do;
@@ -461,14 +494,20 @@ int flash_bwd(const void* qkv, const void* out, const void* dout, const float* l
   p.scale = 0.125f;
   p.scale_log2 = 0.125f * 1.4426950408889634f;
   p.status = status;
-  p.debug = getenv("Z2H_FLASH_DEBUG") ? atoi(getenv("Z2H_FLASH_DEBUG")) : 0;
+  p.drop_p = drop_p;
+  p.seed_ptr = seed_ptr;
+  p.site = site;
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     attr = true;
   }
   const int n_t = (T + TS - 1) / TS;
-  flash_bwd_kernel<<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
+  if (drop_p > 0.f)
+    flash_bwd_kernel<true><<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
+  else
+    flash_bwd_kernel<false><<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
   {
     const long long total = (long long)B * T * (C / 8);
     const int grid = (int)((total + 255) / 256);
@@ -478,8 +517,21 @@ int flash_bwd(const void* qkv, const void* out, const void* dout, const float* l
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+int flash_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+              float* dq_accum, float* stats, int B, int T, int H, int* status, cudaStream_t stream) {
+  return flash_bwd_dropout(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, 0.f, nullptr, 0, status,
+                           stream);
+}
+
 }  // namespace z2h
 
+extern "C" int z2h_flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const float* lse,
+                                     void* dqkv, float* dq_accum, float* stats, int B, int T, int H,
+                                     float drop_p, const unsigned long long* seed_ptr, unsigned int site,
+                                     int* status, void* stream) {
+  return z2h::flash_bwd_dropout(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site,
+                                status, (cudaStream_t)stream);
+}
 extern "C" int z2h_flash_bwd_stats_elems(int B, int T, int H) {
   return 2 * B * H * ((T + 127) / 128 * 128);
 }

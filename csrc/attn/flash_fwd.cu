@@ -18,6 +18,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
+#include "../common/dropout.cuh"
 
 namespace z2h {
 namespace {
@@ -42,8 +43,16 @@ struct FwdParams {
   float scale_log2;  // softmax_scale * log2(e)
   float scale;
   int* status;
+  // attention-probability dropout (DROP instantiation only)
+  float drop_p;
+  const unsigned long long* seed_ptr;
+  uint32_t site;
 };
 
+// DROP: the probabilities that enter P V are masked (mask of element (b, h, q, k): word
+// ((b*H + h)*T + q) * ceil(T/4) + k/4 of the site's stream); the softmax normaliser is not, and the
+// 1/(1-p) scale is applied once to the output row.
+template <bool DROP>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -178,6 +187,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     // across KV tiles, rarely needs rescaling; P stays <= 2^8, well inside bf16 / fp32 range.
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t p_row = smem_u32(sP) + r * 128;
+    DropoutSpec drop = {};
+    unsigned long long drop_row = 0;  // first mask word of this query row
+    if (DROP) {
+      drop = make_dropout_spec(p.seed_ptr, p.site, p.drop_p);
+      drop_row = ((unsigned long long)bh * p.T + (unsigned long long)(qi * QT + r)) *
+                 (unsigned long long)((p.T + 3) / 4);
+    }
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait_bounded(s_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
@@ -242,6 +258,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint32_t pk[4];
+          uint32_t mw[2] = {0, 0};
+          if (DROP) {
+            const unsigned long long w0 = drop_row + (unsigned long long)(j * (KT / 4) + ch * 8 + q * 2);
+            mw[0] = dropout_word(drop.seed_lo, drop.seed_hi, w0);
+            mw[1] = dropout_word(drop.seed_lo, drop.seed_hi, w0 + 1);
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = q * 8 + e * 2;
@@ -253,6 +275,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
             }
             rs0 += p0;
             rs1 += p1;
+            if (DROP) {
+              if (!dropout_keep(mw[e >> 1], (e & 1) * 2, drop.threshold)) p0 = 0.f;
+              if (!dropout_keep(mw[e >> 1], (e & 1) * 2 + 1, drop.threshold)) p1 = 0.f;
+            }
             pk[e] = pack_bf16x2(p0, p1);
           }
           const uint32_t chunk = (uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7);
@@ -282,7 +308,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     }
     const int t = qi * QT + r;
     if (ok && t < p.T) {
-      const float inv = 1.f / l_run;
+      const float inv = DROP ? drop.scale / l_run : 1.f / l_run;
       __nv_bfloat16* op = p.out + (long long)(row0 + t) * p.C + h * HD;
 #pragma unroll
       for (int q = 0; q < HD / 8; ++q) {
@@ -308,8 +334,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
 
 }  // namespace
 
-int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,
-              cudaStream_t stream) {
+int flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int H, float drop_p,
+                      const unsigned long long* seed_ptr, unsigned int site, int* status,
+                      cudaStream_t stream) {
   const int C = H * HD;
   if (B <= 0 || T <= 0) return 0;
   if (reinterpret_cast<uintptr_t>(qkv) & 15 || reinterpret_cast<uintptr_t>(out) & 15) return 1;
@@ -322,18 +349,37 @@ int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* 
   p.scale = 0.125f;
   p.scale_log2 = 0.125f * 1.4426950408889634f;
   p.status = status;
+  if (!(drop_p >= 0.f) || drop_p >= 1.f) return 1;
+  p.drop_p = drop_p;
+  p.seed_ptr = seed_ptr;
+  p.site = site;
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     attr = true;
   }
   const int n_qt = (T + QT - 1) / QT;
-  flash_fwd_kernel<<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
+  if (drop_p > 0.f)
+    flash_fwd_kernel<true><<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
+  else
+    flash_fwd_kernel<false><<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,
+              cudaStream_t stream) {
+  return flash_fwd_dropout(qkv, out, lse, B, T, H, 0.f, nullptr, 0, status, stream);
 }
 
 }  // namespace z2h
 
+extern "C" int z2h_flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int H,
+                                     float drop_p, const unsigned long long* seed_ptr, unsigned int site,
+                                     int* status, void* stream) {
+  return z2h::flash_fwd_dropout(qkv, out, lse, B, T, H, drop_p, seed_ptr, site, status,
+                                (cudaStream_t)stream);
+}
 extern "C" int z2h_flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,
                              void* stream) {
   return z2h::flash_fwd(qkv, out, lse, B, T, H, status, (cudaStream_t)stream);

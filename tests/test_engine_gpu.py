@@ -105,3 +105,49 @@ def test_engine_checkpoint_round_trip(tmp_path):
     b.train_step(nxt, lr=1e-3)
     assert a.read_loss() == pytest.approx(b.read_loss(), abs=1e-4)
     assert torch.allclose(a.p32, b.p32, atol=1e-6)
+
+
+def test_engine_with_dropout_tracks_module_with_the_same_masks():
+    """Dropout 0.2 at all four sites of the reference model: the engine's counter-based masks are
+    restated on the host, so the fp32 PyTorch module can replay the very same masks."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+    from zero_to_hero_b200.models.gpt2 import GPT2
+    from zero_to_hero_b200.ops import _lib
+    from zero_to_hero_b200.optim.adamw import build_optimizer
+
+    cfg = _cfg()
+    cfg.model.dropout = 0.2
+    cfg.model.num_layers = 2
+    eng = GPT2TrainEngine(cfg, "cuda", seed=3)
+    ref = GPT2(cfg.model).float().train()
+    ref.load_state_dict({k: v.cpu() for k, v in eng.state_dict().items()})
+    opt = build_optimizer(ref, cfg.optim, "cpu")
+    g = torch.Generator().manual_seed(0)
+    k = 0
+    for step in range(2):
+        batches = _batches(g)
+        eng.train_step(batches, lr=1e-3)
+        loss_e, gn_e = eng.read_loss(), eng.read_grad_norm()
+        opt.zero_grad()
+        loss_r = 0.0
+        for X, Y in batches:
+            k += 1
+            ref.counter_dropout_seed = eng.dropout_seed_of_micro_step(k)
+            _, l = ref(X, Y)
+            (l / 2).backward()
+            loss_r += l.item() / 2
+        gn_r = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0).item()
+        opt.step()
+        assert loss_e == pytest.approx(loss_r, abs=1e-2)
+        assert gn_e == pytest.approx(gn_r, rel=3e-2)
+    # a run without dropout gives a different loss: the masks really are applied
+    cfg0 = _cfg()
+    cfg0.model.num_layers = 2
+    eng0 = GPT2TrainEngine(cfg0, "cuda", seed=3)
+    eng0.train_step(_batches(torch.Generator().manual_seed(0)), lr=1e-3)
+    eng1 = GPT2TrainEngine(cfg, "cuda", seed=3)
+    eng1.train_step(_batches(torch.Generator().manual_seed(0)), lr=1e-3)
+    assert abs(eng0.read_loss() - eng1.read_loss()) > 1e-3
+    _lib.check_status()

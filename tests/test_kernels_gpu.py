@@ -349,3 +349,58 @@ def test_sample_topk_distribution_and_support(dev):
     seen = set(sample_topk_native(t, 1.0, 2, seed=1).view(-1).tolist())
     assert seen == {1, 2, 3}
     status_ok()
+
+
+# ------------------------------------------------------------------------------ dropout
+@pytest.mark.parametrize("p", [0.1, 0.5])
+def test_dropout_apply_matches_host_mask(dev, p):
+    from zero_to_hero_b200.ops import dropout as D, native as N
+    n = 4096 * 24
+    x = torch.randn(n, device=dev).bfloat16()
+    res = torch.randn(n, device=dev).bfloat16()
+    seed = torch.tensor([987654321], device=dev, dtype=torch.int64)
+    out = torch.empty_like(x)
+    N.dropout_apply(x, out, p, seed, 5, residual=res)
+    keep = D.elementwise_keep(n, p, 987654321, 5, dev)
+    _, scale = D.threshold_and_scale(p)
+    ref = (torch.where(keep, x.float() * scale, torch.zeros((), device=dev)) + res.float()).bfloat16()
+    assert torch.equal(out, ref)
+    frac = 1.0 - keep.float().mean().item()
+    assert abs(frac - round(p * 256) / 256) < 0.01
+    # the backward of a site is the same call on the gradient, in place allowed
+    g = torch.randn(n, device=dev).bfloat16()
+    g_ref = torch.where(keep, g.float() * scale, torch.zeros((), device=dev)).bfloat16()
+    N.dropout_apply(g, g, p, seed, 5)
+    assert torch.equal(g, g_ref)
+    # another site or seed gives another mask
+    assert not torch.equal(keep, D.elementwise_keep(n, p, 987654321, 6, dev))
+
+
+@pytest.mark.parametrize("B,T,H", [(2, 256, 2), (1, 200, 3)])
+def test_flash_attention_dropout_against_masked_reference(dev, B, T, H):
+    from zero_to_hero_b200.ops import dropout as D, native as N
+    p, seed_v, site = 0.25, 4242, 7
+    C = H * 64
+    qkv = (torch.randn(B * T, 3 * C, device=dev) * 0.7).bfloat16()
+    dout = torch.randn(B * T, C, device=dev).bfloat16()
+    seed = torch.tensor([seed_v], device=dev, dtype=torch.int64)
+    out = torch.empty(B * T, C, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev)
+    N.flash_fwd(qkv, out, lse, B, T, H, p, seed, site)
+    dqkv = torch.empty_like(qkv)
+    dq_acc = torch.empty(B * T, C, device=dev)
+    stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
+    N.flash_bwd(qkv, out, dout, lse, dqkv, dq_acc, stats, B, T, H, p, seed, site)
+    # reference: explicit attention in fp32 with the same mask
+    x = qkv.float().view(B, T, 3, H, 64).requires_grad_(True)
+    q, k, v = (x[:, :, i].transpose(1, 2) for i in range(3))
+    att = (q @ k.transpose(-2, -1)) * 0.125
+    causal = torch.ones(T, T, dtype=torch.bool, device=dev).tril()
+    att = att.masked_fill(~causal, float("-inf")).softmax(-1)
+    keep = D.attention_keep(B, H, T, p, seed_v, site, dev)
+    att = att * keep * D.threshold_and_scale(p)[1]
+    ref = (att @ v).transpose(1, 2).reshape(B * T, C)
+    ref.backward(dout.float())
+    assert rel_err(out, ref) < 2e-2
+    assert rel_err(dqkv, x.grad.reshape(B * T, 3 * C)) < 3e-2
+    status_ok()

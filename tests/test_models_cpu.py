@@ -140,3 +140,33 @@ def test_vocab_bigram_masking():
     assert b.generate(X[:, :1], 5).shape == (1, 6)
     a, b2, c = causal_average_variants(torch.randn(2, 6, 3))
     assert torch.allclose(a, b2, atol=1e-6) and torch.allclose(a, c, atol=1e-6)
+
+
+def test_counter_dropout_masks_are_deterministic_and_calibrated():
+    """The host restatement of the kernels' dropout masks: reproducible, site-dependent, and with
+    the requested drop rate (quantised to 1/256); the module can run with those masks on CPU."""
+    import torch
+    from zero_to_hero_b200.config import get_preset
+    from zero_to_hero_b200.models.gpt2 import GPT2
+    from zero_to_hero_b200.ops import dropout as D
+
+    a = D.elementwise_keep(100_000, 0.2, 11, 3)
+    assert torch.equal(a, D.elementwise_keep(100_000, 0.2, 11, 3))
+    assert not torch.equal(a, D.elementwise_keep(100_000, 0.2, 11, 4))
+    assert not torch.equal(a, D.elementwise_keep(100_000, 0.2, 12, 3))
+    assert abs((1 - a.float().mean().item()) - 51 / 256) < 0.01
+    m = D.attention_keep(2, 3, 50, 0.5, 7, 1)
+    assert m.shape == (2, 3, 50, 50) and abs(m.float().mean().item() - 0.5) < 0.03
+    assert D.threshold_and_scale(0.001) == (0, 1.0)  # below 1/512: nothing is dropped
+
+    cfg = get_preset("gpt2-tiny").model
+    cfg.dropout = 0.3
+    torch.manual_seed(0)
+    model = GPT2(cfg).train()
+    X = torch.randint(0, cfg.vocab_size, (2, 16))
+    model.counter_dropout_seed = 5
+    l1 = model(X, X)[1].item()
+    l2 = model(X, X)[1].item()
+    model.counter_dropout_seed = 6
+    l3 = model(X, X)[1].item()
+    assert l1 == l2 and l1 != l3

@@ -111,8 +111,8 @@ class GPT2TrainEngine:
             raise ValueError("the fused engine implements the GPT-2 architecture")
         if mc.head_dim != 64:
             raise ValueError("the flash-attention kernels are written for head_dim 64")
-        if mc.dropout != 0.0:
-            raise ValueError("the fused engine runs without dropout; use the module path for dropout")
+        if not 0.0 <= mc.dropout < 1.0:
+            raise ValueError("dropout must be in [0, 1)")
         if mc.emb_dim % 8 or mc.emb_dim > 2048:
             raise ValueError("emb_dim must be a multiple of 8 and at most 2048")
         self.cfg = cfg
@@ -147,11 +147,12 @@ class GPT2TrainEngine:
         self.loss_accum = torch.zeros(1, device=dev, dtype=f32)
         self.loss_host = torch.zeros(1, dtype=f32).pin_memory()
         self.opt_step = 0
+        self.seed_value = cfg.train.seed if seed is None else seed
         self._alloc_activations(cfg.train.micro_batch, mc.block_size)
         self._graph = None
         self._graph_scale = None
         self.launches_per_micro_step = 0
-        self.init_weights(cfg.train.seed if seed is None else seed)
+        self.init_weights(self.seed_value)
 
     # ------------------------------------------------------------------ parameters
     def init_weights(self, seed: int) -> None:
@@ -243,6 +244,15 @@ class GPT2TrainEngine:
         # backward scratch
         self.d_resid = buf(M, C)
         self.d_c = buf(M, C)
+        # dropout (the reference trains with 0.2): masks are a function of (seed, site, index),
+        # the seed lives on the device so that a captured graph sees a new one at every replay
+        self.drop_p = float(mc.dropout)
+        self.drop_seed0 = int(self.seed_value) * 1_000_003 + 12345 + self.rank
+        self.drop_seed = torch.full((1,), self.drop_seed0, device=dev, dtype=torch.int64)
+        self.micro_steps_done = 0
+        if self.drop_p > 0.0:
+            self.drop_tmp = buf(M, C)  # projection output before dropout + residual
+            self.d_drop = buf(M, C)    # gradient of that output
         self.d_4c = buf(M, 4 * C)
         self.d_qkv = buf(M, 3 * C)
         self.dq_accum = buf(M, C, dtype=f32)
@@ -278,24 +288,41 @@ class GPT2TrainEngine:
             return gw(name) if has_lnb else None
 
         # ---------------- forward
+        pd, seed = self.drop_p, self.drop_seed
         N.embed_fwd(self.idx, w("transformer.wte.weight"), w("transformer.wpe.weight"),
                     self.resid[0], T)
         self._n += 1
+        if pd > 0.0:
+            N.dropout_apply(self.resid[0], self.resid[0], pd, seed, 0)
+            self._n += 1
         for l in range(L):
             p = f"transformer.h.{l}."
             st = self.stats[l]
             N.layernorm_fwd(self.resid[l], w(p + "ln_1.weight"), lnb(p + "ln_1.bias"), self.xn1[l],
                             st[0], st[1])
             G.gemm(self.xn1[l], w(p + "attn.c_attn.weight"), self.qkv[l], bias=w(p + "attn.c_attn.bias"))
-            N.flash_fwd(self.qkv[l], self.att[l], self.lse[l], B, T, H)
-            G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.x_mid[l],
-                   bias=w(p + "attn.c_proj.bias"), residual=self.resid[l], epi=G.EPI_RESIDUAL)
+            N.flash_fwd(self.qkv[l], self.att[l], self.lse[l], B, T, H, pd, seed, 1 + 3 * l)
+            if pd > 0.0:
+                G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.drop_tmp,
+                       bias=w(p + "attn.c_proj.bias"))
+                N.dropout_apply(self.drop_tmp, self.x_mid[l], pd, seed, 2 + 3 * l, residual=self.resid[l])
+                self._n += 1
+            else:
+                G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.x_mid[l],
+                       bias=w(p + "attn.c_proj.bias"), residual=self.resid[l], epi=G.EPI_RESIDUAL)
             N.layernorm_fwd(self.x_mid[l], w(p + "ln_2.weight"), lnb(p + "ln_2.bias"), self.xn2[l],
                             st[2], st[3])
             G.gemm(self.xn2[l], w(p + "mlp.c_fc.weight"), self.act[l], bias=w(p + "mlp.c_fc.bias"),
                    aux_out=self.pre[l], epi=G.EPI_GELU)
-            G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.resid[l + 1],
-                   bias=w(p + "mlp.c_proj.bias"), residual=self.x_mid[l], epi=G.EPI_RESIDUAL)
+            if pd > 0.0:
+                G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.drop_tmp,
+                       bias=w(p + "mlp.c_proj.bias"))
+                N.dropout_apply(self.drop_tmp, self.resid[l + 1], pd, seed, 3 + 3 * l,
+                                residual=self.x_mid[l])
+                self._n += 1
+            else:
+                G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.resid[l + 1],
+                       bias=w(p + "mlp.c_proj.bias"), residual=self.x_mid[l], epi=G.EPI_RESIDUAL)
             self._n += 7
         N.layernorm_fwd(self.resid[L], w("transformer.ln_f.weight"), lnb("transformer.ln_f.bias"),
                         self.xf, self.stats_f[0], self.stats_f[1])
@@ -317,10 +344,16 @@ class GPT2TrainEngine:
         for l in reversed(range(L)):
             p = f"transformer.h.{l}."
             st = self.stats[l]
-            # MLP
-            self._wgrad(self.d_resid, self.act[l], p + "mlp.c_proj.weight")
-            N.colsum_bf16(self.d_resid, gw(p + "mlp.c_proj.bias"))
-            G.gemm(self.d_resid, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
+            # MLP (the gradient of the projection output is the residual gradient through the
+            # dropout mask of the forward pass)
+            dy = self.d_resid
+            if pd > 0.0:
+                N.dropout_apply(self.d_resid, self.d_drop, pd, seed, 3 + 3 * l)
+                dy = self.d_drop
+                self._n += 1
+            self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
+            N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
+            G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
                    aux_in=self.pre[l], epi=G.EPI_GELU_GRAD)
             self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
             N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
@@ -329,11 +362,16 @@ class GPT2TrainEngine:
                             self.d_resid, self.d_resid, gw(p + "ln_2.weight"), glnb(p + "ln_2.bias"),
                             self.ln_scratch)
             # attention
-            self._wgrad(self.d_resid, self.att[l], p + "attn.c_proj.weight")
-            N.colsum_bf16(self.d_resid, gw(p + "attn.c_proj.bias"))
-            G.gemm(self.d_resid, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
+            dy = self.d_resid
+            if pd > 0.0:
+                N.dropout_apply(self.d_resid, self.d_drop, pd, seed, 2 + 3 * l)
+                dy = self.d_drop
+                self._n += 1
+            self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
+            N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
+            G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
             N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
-                        self.attn_stats, B, T, H)
+                        self.attn_stats, B, T, H, pd, seed, 1 + 3 * l)
             self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
             N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)
@@ -341,10 +379,18 @@ class GPT2TrainEngine:
                             self.d_resid, self.d_resid, gw(p + "ln_1.weight"), glnb(p + "ln_1.bias"),
                             self.ln_scratch)
             self._n += 4 + 4 + 2 * 2 + 3  # dgrad GEMMs, column sums, LN bwd (2 kernels each), flash bwd (3)
+        if pd > 0.0:
+            N.dropout_apply(self.d_resid, self.d_resid, pd, seed, 0)
+            self._n += 1
         N.embed_bwd(self.idx, self.d_resid, gw("transformer.wte.weight"),
                     gw("transformer.wpe.weight"), B, T)
         self._n += 2
         self.launches_per_micro_step = self._n
+
+    def dropout_seed_of_micro_step(self, k: int) -> int:
+        """Seed of the dropout masks of the k-th micro-step this engine ran (k = 1, 2, ...); give it
+        to `GPT2.counter_dropout_seed` to reproduce that micro-step with the PyTorch module."""
+        return self.drop_seed0 + k * 0x9E3779B1
 
     # ------------------------------------------------------------------ public stepping API
     def micro_steps_per_step(self) -> int:
@@ -357,6 +403,9 @@ class GPT2TrainEngine:
         tensors of shape [micro_batch, block_size]. Gradients accumulate in the flat buffer."""
         self.idx.copy_(idx, non_blocking=True)
         self.tgt.copy_(tgt, non_blocking=True)
+        self.micro_steps_done += 1
+        if self.drop_p > 0.0:
+            self.drop_seed.add_(0x9E3779B1)  # new masks for this micro-step (also under graph replay)
         grad_scale = 1.0 / (self.M * accum_steps * self.world)
         loss_scale = 1.0 / (self.M * accum_steps)
         if not self.cfg.train.use_cuda_graph:

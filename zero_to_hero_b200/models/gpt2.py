@@ -22,6 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..config import ModelConfig
+from ..ops import dropout as D
 from ..ops import functional as Z
 
 
@@ -36,6 +37,26 @@ class LayerNorm(nn.Module):
         return Z.layer_norm(x, self.weight, self.bias, self.eps)
 
 
+def _counter_dropout(x: torch.Tensor, p: float, seed: int, site: int) -> torch.Tensor:
+    """Dropout with the counter-based mask the fused engine's kernels use (ops/dropout.py)."""
+    keep = D.elementwise_keep(x.numel(), p, seed, site, x.device).view(x.shape)
+    return x * (keep.to(x.dtype) * D.threshold_and_scale(p)[1])
+
+
+def _counter_dropout_attention(qkv: torch.Tensor, num_heads: int, p: float, seed: int, site: int):
+    """Plain causal attention whose probabilities are dropped with the engine's mask."""
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    hd = C // num_heads
+    q, k, v = (t.view(B, T, num_heads, hd).transpose(1, 2) for t in qkv.split(C, dim=-1))
+    att = (q @ k.transpose(-2, -1)) * hd ** -0.5
+    causal = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
+    att = att.masked_fill(~causal, float("-inf")).softmax(dim=-1)
+    keep = D.attention_keep(B, num_heads, T, p, seed, site, qkv.device)
+    att = att * (keep.to(att.dtype) * D.threshold_and_scale(p)[1])
+    return (att @ v).transpose(1, 2).contiguous().view(B, T, C)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
@@ -45,9 +66,16 @@ class Attention(nn.Module):
         self.num_heads = cfg.num_heads
         self.dropout = cfg.dropout
 
-    def forward(self, x, residual):
+    def forward(self, x, residual, cdrop=None):
+        """`cdrop` = (seed, layer) selects the counter-based masks of the fused engine instead
+        of torch's generator, so that the module reproduces an engine step exactly."""
         qkv = Z.linear(x, self.c_attn.weight, self.c_attn.bias)
         p = self.dropout if self.training else 0.0
+        if p > 0.0 and cdrop is not None:
+            seed, layer = cdrop
+            y = _counter_dropout_attention(qkv, self.num_heads, p, seed, 1 + 3 * layer)
+            y = Z.linear(y, self.c_proj.weight, self.c_proj.bias)
+            return residual + _counter_dropout(y, p, seed, 2 + 3 * layer)
         y = Z.causal_attention(qkv, self.num_heads, dropout_p=p)
         if p > 0.0:
             y = Z.linear(y, self.c_proj.weight, self.c_proj.bias)
@@ -62,10 +90,12 @@ class MLP(nn.Module):
         self.c_proj = nn.Linear(expansion * cfg.emb_dim, cfg.emb_dim)
         self.dropout = cfg.dropout
 
-    def forward(self, x, residual):
+    def forward(self, x, residual, cdrop=None):
         h = Z.linear(x, self.c_fc.weight, self.c_fc.bias, act="gelu_tanh")
         if self.training and self.dropout > 0.0:
             y = Z.linear(h, self.c_proj.weight, self.c_proj.bias)
+            if cdrop is not None:
+                return residual + _counter_dropout(y, self.dropout, cdrop[0], 3 + 3 * cdrop[1])
             return residual + F.dropout(y, self.dropout, True)
         return Z.linear(h, self.c_proj.weight, self.c_proj.bias, residual=residual)
 
@@ -78,9 +108,9 @@ class Block(nn.Module):
         self.ln_2 = LayerNorm(cfg.emb_dim, cfg.ln_bias)
         self.mlp = MLP(cfg)
 
-    def forward(self, x):
-        x = self.attn(self.ln_1(x), x)  # pre-norm; the residual add is fused into the projection
-        x = self.mlp(self.ln_2(x), x)
+    def forward(self, x, cdrop=None):
+        x = self.attn(self.ln_1(x), x, cdrop)  # pre-norm; the residual add is fused into the projection
+        x = self.mlp(self.ln_2(x), x, cdrop)
         return x
 
 
@@ -100,6 +130,9 @@ class GPT2(nn.Module):
         self.transformer = Transformer(config)
         self.lm_head = nn.Linear(config.emb_dim, config.vocab_size, bias=False)
         self.lm_head.weight = self.transformer.wte.weight  # weight tying
+        # None: torch's generator drives dropout. An integer: the counter-based masks of the fused
+        # engine with that seed (GPT2TrainEngine.dropout_seed_of_micro_step gives the engine's).
+        self.counter_dropout_seed: int | None = None
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -123,10 +156,12 @@ class GPT2(nn.Module):
         assert T <= self.config.block_size, "sequence longer than block_size"
         tr = self.transformer
         x = Z.embedding(X, tr.wte.weight, tr.wpe.weight)
+        seed = self.counter_dropout_seed
         if self.training and self.config.dropout > 0.0:
-            x = F.dropout(x, self.config.dropout, True)
-        for block in tr.h:
-            x = block(x)
+            x = F.dropout(x, self.config.dropout, True) if seed is None else \
+                _counter_dropout(x, self.config.dropout, seed, 0)
+        for layer, block in enumerate(tr.h):
+            x = block(x, None if seed is None else (seed, layer))
         return tr.ln_f(x)
 
     def forward(self, X: torch.Tensor, Y: torch.Tensor | None = None):

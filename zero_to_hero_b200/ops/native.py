@@ -32,6 +32,12 @@ _sigs = {
     "z2h_cast_f32_to_bf16": [c_void_p, c_void_p, c_longlong, c_void_p],
     "z2h_flash_fwd": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "z2h_flash_bwd": [c_void_p] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p],
+    "z2h_flash_fwd_dropout": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                              ctypes.c_uint, c_void_p, c_void_p],
+    "z2h_flash_bwd_dropout": [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_void_p, ctypes.c_uint,
+                                               c_void_p, c_void_p],
+    "z2h_dropout_apply": [c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_void_p, ctypes.c_uint,
+                          c_void_p],
 }
 _fns: dict[str, ctypes._CFuncPtr] = {}
 
@@ -122,7 +128,15 @@ def cast_f32_to_bf16(src, dst):
     _check(_f("z2h_cast_f32_to_bf16")(ptr(src), ptr(dst), src.numel(), stream_ptr()), "cast")
 
 
-def flash_fwd(qkv, out, lse, B, T, H):
+def flash_fwd(qkv, out, lse, B, T, H, drop_p: float = 0.0, seed=None, site: int = 0):
+    """Causal attention forward. With `drop_p` > 0 the attention probabilities are dropped with
+    the mask of (`seed` [int64 device tensor of one element], `site`); see ops/dropout.py."""
+    if drop_p > 0.0:
+        assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
+        _check(_f("z2h_flash_fwd_dropout")(ptr(qkv), ptr(out), ptr(lse), B, T, H, drop_p, ptr(seed), site,
+                                           ptr(_lib.status_word(out.device)), stream_ptr()),
+               "flash_fwd_dropout")
+        return
     _check(_f("z2h_flash_fwd")(ptr(qkv), ptr(out), ptr(lse), B, T, H,
                                ptr(_lib.status_word(out.device)), stream_ptr()), "flash_fwd")
 
@@ -132,8 +146,28 @@ def flash_bwd_stats_elems(B: int, T: int, H: int) -> int:
     return 2 * B * H * ((T + 127) // 128 * 128)
 
 
-def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H):
+def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p: float = 0.0, seed=None,
+              site: int = 0):
     assert stats.numel() >= flash_bwd_stats_elems(B, T, H)
+    if drop_p > 0.0:
+        assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
+        _check(_f("z2h_flash_bwd_dropout")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                           ptr(dq_accum), ptr(stats), B, T, H, drop_p, ptr(seed), site,
+                                           ptr(_lib.status_word(out.device)), stream_ptr()),
+               "flash_bwd_dropout")
+        return
     _check(_f("z2h_flash_bwd")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), ptr(dq_accum),
                                ptr(stats), B, T, H, ptr(_lib.status_word(out.device)),
                                stream_ptr()), "flash_bwd")
+
+
+def dropout_apply(x, out, drop_p: float, seed, site: int, residual=None):
+    """out = dropout(x) (+ residual) over contiguous bf16 tensors; `out` may be `x`. The mask is a
+    function of (seed[0], site, element index): applying the call to a gradient with the same seed
+    and site is the backward of the forward call (ops/dropout.py restates the mask on the host)."""
+    assert x.is_contiguous() and out.is_contiguous() and x.dtype == torch.bfloat16
+    assert seed.dtype == torch.int64 and seed.is_cuda
+    if residual is not None:
+        assert residual.is_contiguous() and residual.numel() == x.numel()
+    _check(_f("z2h_dropout_apply")(ptr(x), ptr(residual), ptr(out), x.numel(), drop_p, ptr(seed), site,
+                                   stream_ptr()), "dropout_apply")
