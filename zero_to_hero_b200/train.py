@@ -8,7 +8,7 @@ One code path covers the reference's single-GPU trainer (nn/gpt2/train.py), its 
 (nn/gpt2/train_ddp.py) and the char-level script (nn/gpt/3_gpt.py:152-248):
   * `train.dtype=bf16` on a GPU with a GPT-2 model runs the fused engine (hand-scheduled
     kernels, CUDA graph, fused peer-memory all-reduce + AdamW across ranks);
-  * anything else (CPU, fp32, the char model, dropout > 0) runs the PyTorch module path with
+  * anything else (CPU, fp32, the char model) runs the PyTorch module path with
     torch AdamW (and torch DDP when launched with several ranks).
 Adds what the reference lacks: gradient accumulation to `train.total_batch_tokens`, periodic
 checkpoints, resume, JSONL logs. Tokens/sec is device-timed (CUDA events) per logging window.
@@ -73,8 +73,7 @@ def train(cfg: Config, resume: str = "") -> dict:
     mc, tc, oc = cfg.model, cfg.train, cfg.optim
     tokens_per_micro = tc.micro_batch * mc.block_size * world
     accum = max(1, tc.total_batch_tokens // tokens_per_micro)
-    fused = (device.type == "cuda" and tc.dtype == "bf16" and mc.kind == "gpt2"
-             and mc.dropout == 0.0 and mc.head_dim == 64)
+    fused = (device.type == "cuda" and tc.dtype == "bf16" and mc.kind == "gpt2" and mc.head_dim == 64)
     logger = StepLogger(tc.log_jsonl, master)
     if master:
         print(cfg.to_json())
