@@ -68,11 +68,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* v_full = k_full + KV_STAGES;
-  uint64_t* kv_empty = v_full + KV_STAGES;
-  uint64_t* s_full = kv_empty + KV_STAGES;
+  uint64_t* k_empty = v_full + KV_STAGES;   // K stage free: the score MMAs that read it are done
+  uint64_t* v_empty = k_empty + KV_STAGES;  // V stage free: the P V MMAs that read it are done
+  uint64_t* s_full = v_empty + KV_STAGES;
   uint64_t* p_full = s_full + 1;
-  uint64_t* pv_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
+  uint64_t* pv_full = p_full + 1;   // completes once per KV tile, when P V of that tile is done
+  uint64_t* s_read = pv_full + 1;   // the softmax warps have the score tile in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_read + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,11 +91,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(p_full, 4);
     mbar_init(pv_full, 1);
+    mbar_init(s_read, 4);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -111,14 +115,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, TILE_BYTES);
       tma_load_2d(sQ, &tm_qkv, q_full, h * HD, row0 + qi * QT);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
-        mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
-        tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &k_full[s], p.C + h * HD, row0 + j * KT);
-        mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
-        tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &v_full[s], 2 * p.C + h * HD, row0 + j * KT);
+      // K tiles run one tile ahead of V tiles: a K stage is free as soon as its scores are
+      // computed, a V stage only after P V, and the scores of tile j+1 are wanted early
+      for (int j = 0; j <= n_kv; ++j) {
+        if (j < n_kv) {
+          const int s = j % KV_STAGES;
+          const uint32_t ph = (j / KV_STAGES) & 1;
+          if (!mbar_wait_bounded(&k_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
+          mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+          tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &k_full[s], p.C + h * HD, row0 + j * KT);
+        }
+        if (j > 0) {
+          const int jv = j - 1, s = jv % KV_STAGES;
+          const uint32_t ph = (jv / KV_STAGES) & 1;
+          if (!mbar_wait_bounded(&v_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
+          mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+          tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &v_full[s], 2 * p.C + h * HD, row0 + jv * KT);
+        }
       }
       if (*abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -148,10 +161,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
           tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(k_desc[0], k * 32),
                         idesc_s, k > 0);
         tc_commit(s_full);
+        tc_commit(&k_empty[0]);
       }
+      // Per KV tile j: the scores of tile j+1 are issued as soon as the softmax warps hold tile j
+      // in registers, i.e. while they still work on it, and only then P V of tile j. The softmax
+      // chain therefore never waits for an MMA of its own tile: S is ready a tile ahead and P V
+      // runs behind it.
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
+        if (j + 1 < n_kv) {
+          const int s2 = (j + 1) % KV_STAGES;
+          const uint32_t ph2 = ((j + 1) / KV_STAGES) & 1;
+          if (!mbar_wait_bounded(s_read, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
+          if (!mbar_wait_bounded(&k_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
+          tc_fence_after();
+          const uint64_t kd = s2 == 0 ? k_desc[0] : k_desc[1];
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k)
+            tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(kd, k * 32),
+                          idesc_s, k > 0);
+          tc_commit(s_full);
+          tc_commit(&k_empty[s2]);
+        }
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
         if (!mbar_wait_bounded(&v_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
         tc_fence_after();
@@ -162,20 +194,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
                         desc_advance(p_desc, (k >> 2) * (QT * 128) + (k & 3) * 32),
                         desc_advance(vd, k * 2048), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        if (j == n_kv - 1) tc_commit(pv_full);
-        tc_commit(&kv_empty[s]);
-        if (j + 1 < n_kv) {
-          const int s2 = (j + 1) % KV_STAGES;
-          const uint32_t ph2 = ((j + 1) / KV_STAGES) & 1;
-          if (!mbar_wait_bounded(&k_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
-          tc_fence_after();
-          const uint64_t kd = s2 == 0 ? k_desc[0] : k_desc[1];
-#pragma unroll
-          for (int k = 0; k < HD / 16; ++k)
-            tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(kd, k * 32),
-                          idesc_s, k > 0);
-          tc_commit(s_full);
-        }
+        tc_commit(pv_full);
+        tc_commit(&v_empty[s]);
       }
     }
   } else {
@@ -207,6 +227,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
 #pragma unroll
       for (int ch = 0; ch < KT / 32; ++ch) tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, sv[ch]);
       tmem_ld_wait();
+      // the score columns may be overwritten with the next tile from here on
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_read);
       float m_new = m_run;
       if (!diag) {
         float m0 = m_new, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
@@ -228,7 +252,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       if (j == 0) {
         m_run = m_new;  // nothing accumulated yet
       } else {
-        // s_full(j) was committed after P V of tile j-1, so O in TMEM is complete here
+        // P V of tile j-1 must be complete before O is rescaled and before P is overwritten
+        if (!mbar_wait_bounded(pv_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         const bool grow = (m_new - m_run) * p.scale_log2 > 8.f;
         if (__any_sync(0xffffffffu, grow)) {
           const float alpha = grow ? ex2_fast((m_run - m_new) * p.scale_log2) : 1.f;
@@ -293,7 +322,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);  // one arrival per softmax warp
     }
-    if (ok && !mbar_wait_bounded(pv_full, 0, abort_flag, p.status, kTimeoutTmemFull)) ok = false;
+    if (ok && !mbar_wait_bounded(pv_full, (n_kv - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) ok = false;
     tc_fence_after();
     float o[HD];
     if (ok) {
