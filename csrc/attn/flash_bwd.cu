@@ -19,6 +19,7 @@
 //
 // This is the hand-written counterpart of what autograd runs for
 // F.scaled_dot_product_attention in the reference (nn/gpt2/modules.py:37, train_ddp.py:141).
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                  const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  pdl_launch_dependents();
   if (smem_u32(smem_raw) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
     return;
@@ -117,6 +119,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -402,6 +405,8 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
                                       const __nv_bfloat16* __restrict__ dout,
                                       const float* __restrict__ lse, float* __restrict__ stats,
                                       float* __restrict__ dq_accum, int B, int T, int H, int Tpad) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)B * T * H * 8;
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const bool valid = idx < total;  // every lane stays until after the shuffles
@@ -448,6 +453,8 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
 __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
                                             __nv_bfloat16* __restrict__ dqkv, long long M, int C,
                                             float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = C / 8;
   const long long total = M * vec_per_row;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -483,8 +490,8 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
     const long long npad = 2LL * B * H * (Tpad - T);
     if (npad > total) total = npad;
     const int grid = (int)((total + 255) / 256);
-    flash_bwd_prep_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
-                                                  lse, stats, dq_accum, B, T, H, Tpad);
+    launch_kernel(flash_bwd_prep_kernel, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)out,
+                  (const __nv_bfloat16*)dout, lse, stats, dq_accum, B, T, H, Tpad);
   }
   BwdParams p;
   p.stats = stats; p.Tpad = Tpad;
@@ -504,15 +511,13 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
     attr = true;
   }
   const int n_t = (T + TS - 1) / TS;
-  if (drop_p > 0.f)
-    flash_bwd_kernel<true><<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
-  else
-    flash_bwd_kernel<false><<<B * H * n_t, NUM_THREADS, SMEM_BYTES, stream>>>(tm_qkv, tm_do, p);
+  launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H * n_t),
+                dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm_qkv, tm_do, p);
   {
     const long long total = (long long)B * T * (C / 8);
     const int grid = (int)((total + 255) / 256);
-    flash_bwd_dq_convert_kernel<<<grid, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dqkv,
-                                                        (long long)B * T, C, 0.125f);
+    launch_kernel(flash_bwd_dq_convert_kernel, dim3(grid), dim3(256), 0, stream, true, (const float*)dq_accum,
+                  (__nv_bfloat16*)dqkv, (long long)B * T, C, 0.125f);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -15,6 +15,7 @@
 //              there only when a row maximum grows by more than 2^8.
 // TMEM use is 192 columns (allocated as 256) and shared memory ~113 KiB, so two CTAs share an
 // SM and one CTA's tensor-core work overlaps the other's exponentials.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
@@ -56,6 +57,7 @@ template <bool DROP>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  pdl_launch_dependents();
   if (smem_u32(smem_raw) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, (int)kBadArgument);
     return;
@@ -110,6 +112,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -389,11 +392,9 @@ int flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int 
     attr = true;
   }
   const int n_qt = (T + QT - 1) / QT;
-  if (drop_p > 0.f)
-    flash_fwd_kernel<true><<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
-  else
-    flash_fwd_kernel<false><<<B * H * n_qt, NUM_THREADS, SMEM_BYTES, stream>>>(tm, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+  const cudaError_t err = launch_kernel(drop_p > 0.f ? flash_fwd_kernel<true> : flash_fwd_kernel<false>,
+                                        dim3(B * H * n_qt), dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm, p);
+  return err == cudaSuccess ? 0 : 3;
 }
 
 int flash_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int* status,

@@ -107,6 +107,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 }
 
 // ----------------------------------------------------------------------------------------
+// Programmatic dependent launch (see launch.cuh)
+// ----------------------------------------------------------------------------------------
+// Lets the next kernel in the stream start being scheduled; placed first in every kernel.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Returns once every kernel this one depends on has completed and its writes are visible; placed
+// before the first access to global memory (a no-op for a kernel launched in plain stream order).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies; loads carry no cluster multicast anywhere in this tree)
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {

@@ -3,6 +3,7 @@
 // reference) and their backward, which is the same kernel applied to the gradient.
 // bf16 in and out, 8 elements (two mask words) per thread, in place allowed.
 #include "../common/dropout.cuh"
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "dropout.h"
 
@@ -13,6 +14,8 @@ __global__ void __launch_bounds__(256)
 dropout_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                      __nv_bfloat16* __restrict__ out, long long n_vec, float p,
                      const unsigned long long* __restrict__ seed_ptr, uint32_t site) {
+  pdl_launch_dependents();
+  pdl_wait();
   const DropoutSpec d = make_dropout_spec(seed_ptr, site, p);
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < n_vec;
        v += (long long)gridDim.x * blockDim.x) {
@@ -52,7 +55,7 @@ int dropout_apply(const void* x, const void* residual, void* out, long long n, f
   const long long n_vec = n / 8;
   long long blocks = (n_vec + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  dropout_apply_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)residual,
+  launch_kernel(dropout_apply_kernel, dim3((int)blocks), dim3(256), 0, stream, true, (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual,
                                                        (__nv_bfloat16*)out, n_vec, p, seed_ptr, site);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -8,6 +8,7 @@
 // Out-of-range token ids are clamped into the table and counted in the status word instead
 // of faulting (the reference kernel bounds-checks ids as well, gpu-mojo/problems/p21/op/
 // embedding.mojo:13-60); the model-level semantics are nn/gpt2/modules.py:104-107.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "embed.h"
 
@@ -18,6 +19,8 @@ template <typename IdxT>
 __global__ void embed_fwd_kernel(const IdxT* __restrict__ idx, const __nv_bfloat16* __restrict__ wte,
                                  const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out,
                                  int M, int T, int C, int V, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = C / 8;
   const long long total = (long long)M * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -50,6 +53,8 @@ __global__ void embed_fwd_kernel(const IdxT* __restrict__ idx, const __nv_bfloat
 template <typename IdxT>
 __global__ void embed_bwd_wte_kernel(const IdxT* __restrict__ idx, const __nv_bfloat16* __restrict__ dx,
                                      float* __restrict__ dwte, int M, int C, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec_per_row = C / 4;
   const long long total = (long long)M * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -68,6 +73,8 @@ __global__ void embed_bwd_wte_kernel(const IdxT* __restrict__ idx, const __nv_bf
 
 __global__ void embed_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dx, float* __restrict__ dwpe,
                                      int B, int T, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)T * C;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -86,11 +93,11 @@ int embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, 
   const long long total = (long long)M * (C / 8);
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (idx_is_64)
-    embed_fwd_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)idx, (const __nv_bfloat16*)wte,
+    launch_kernel(embed_fwd_kernel<long long>, dim3(grid), dim3(256), 0, stream, true, (const long long*)idx, (const __nv_bfloat16*)wte,
                                                          (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out,
                                                          M, T, C, V, status);
   else
-    embed_fwd_kernel<int><<<grid, 256, 0, stream>>>((const int*)idx, (const __nv_bfloat16*)wte,
+    launch_kernel(embed_fwd_kernel<int>, dim3(grid), dim3(256), 0, stream, true, (const int*)idx, (const __nv_bfloat16*)wte,
                                                    (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out, M,
                                                    T, C, V, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
@@ -104,15 +111,15 @@ int embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float
   const long long total = (long long)M * (C / 4);
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (idx_is_64)
-    embed_bwd_wte_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)idx,
+    launch_kernel(embed_bwd_wte_kernel<long long>, dim3(grid), dim3(256), 0, stream, true, (const long long*)idx,
                                                              (const __nv_bfloat16*)dx, dwte, M, C, V);
   else
-    embed_bwd_wte_kernel<int><<<grid, 256, 0, stream>>>((const int*)idx, (const __nv_bfloat16*)dx,
+    launch_kernel(embed_bwd_wte_kernel<int>, dim3(grid), dim3(256), 0, stream, true, (const int*)idx, (const __nv_bfloat16*)dx,
                                                        dwte, M, C, V);
   if (dwpe != nullptr) {
     const long long tc = (long long)T * C;
     const int g2 = (int)((tc + 255) / 256 < 148 * 16 ? (tc + 255) / 256 : 148 * 16);
-    embed_bwd_wpe_kernel<<<g2, 256, 0, stream>>>((const __nv_bfloat16*)dx, dwpe, B, T, C);
+    launch_kernel(embed_bwd_wpe_kernel, dim3(g2), dim3(256), 0, stream, true, (const __nv_bfloat16*)dx, dwpe, B, T, C);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -20,6 +20,7 @@
 //
 // Replaces the nn.Linear calls of the reference model (nn/gpt2/modules.py:21-22,49-51,82) and
 // their autograd; the reference's own tensor-core kernel is gpu-mojo/problems/p33/p33.mojo:130-245.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "gemm.h"
@@ -68,6 +69,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 #ifdef Z2H_GEMM_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 64) g_epi_n = 0;
 #endif
@@ -98,6 +100,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above overlaps the previous kernel's tail; global memory from here on
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -280,8 +283,9 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
   int grid = tiles < num_sms ? (int)tiles : num_sms;
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   if (grid < 1) return 0;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+  return launch_kernel(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, true, tmA, tmB, p) == cudaSuccess
+             ? 0
+             : 3;
 }
 
 }  // namespace

@@ -13,6 +13,7 @@
 // tcgen05.commit arrivals multicast to the same barrier offset in both CTAs. The epilogue
 // warps of both CTAs arrive on the even CTA's "accumulator drained" barrier.
 // Warp roles, epilogues, split-K and operand layouts are those of gemm_tcgen05.cu.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "gemm.h"
@@ -57,6 +58,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
   const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs), 1 = peer
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
@@ -93,6 +95,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above overlaps the previous kernel's tail; global memory from here on
 
   if (warp == 0) {
     // ------------------------------ TMA producer (one per CTA) ------------------------------
@@ -279,13 +282,15 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? 0 : 3;
 }
 

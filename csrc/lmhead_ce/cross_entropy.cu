@@ -12,6 +12,7 @@
 // Semantics: F.cross_entropy(logits.view(B*T, V), Y.view(B*T)) as in nn/gpt2/modules.py:115-117
 // (mean over rows is applied through grad_scale and by the caller for the loss); the fused
 // backward is the identity derived by hand in nn/makemore/3_1_backprop.py:222-231.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "ce.h"
 
@@ -62,6 +63,8 @@ __global__ void __launch_bounds__(kRowThreads)
 ce_row_in_smem_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ targets,
                       float* __restrict__ losses, int V_real, int V_pad, long long ld, float grad_scale,
                       int write_grad, int ignore_index, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float sh[32];
   __shared__ __align__(8) uint64_t bar;
@@ -106,33 +109,13 @@ ce_row_in_smem_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict
   }
   m = cta_reduce<true>(m, sh);
   const float m2 = m * kLog2e;
-  // ---- sum of exponentials
+  // The target logit is needed for the loss and the row is about to be overwritten in place.
+  const float tgt_logit =
+      ignored ? 0.f : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(smem)[tgt]);
+  __syncthreads();
+  // ---- sum of exponentials; e = exp(x - max) replaces x in shared memory as bf16, so that the
+  // gradient pass needs no second exponential (its result is rounded to bf16 anyway)
   float s = 0.f;
-  for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
-    const uint4 u = sv[v];
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = unpack_bf16x2(w[j]);
-      const float e0 = ex2_fast(fmaf(f.x, kLog2e, -m2)), e1 = ex2_fast(fmaf(f.y, kLog2e, -m2));
-      if (v < vlast) {
-        s += e0 + e1;
-      } else {
-        const int c = v * 8 + 2 * j;
-        if (c < V_real) s += e0;
-        if (c + 1 < V_real) s += e1;
-      }
-    }
-  }
-  s = cta_reduce<false>(s, sh);
-  const float lse = m + __logf(s);
-  if (threadIdx.x == 0 && losses != nullptr)
-    losses[row] = ignored ? 0.f : lse - __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(smem)[tgt]);
-  if (!write_grad) return;
-  __syncthreads();  // the target logit has been read before anybody overwrites the row
-  // ---- gradient, in place
-  const float gs = ignored ? 0.f : grad_scale;
-  const float lse2 = lse * kLog2e;
   uint4* sw = reinterpret_cast<uint4*>(smem);
   for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
     uint4 u = sw[v];
@@ -140,15 +123,43 @@ ce_row_in_smem_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 f = unpack_bf16x2(w[j]);
-      const int c = v * 8 + 2 * j;
-      float g0 = (ex2_fast(fmaf(f.x, kLog2e, -lse2)) - (c == tgt ? 1.f : 0.f)) * gs;
-      float g1 = (ex2_fast(fmaf(f.y, kLog2e, -lse2)) - (c + 1 == tgt ? 1.f : 0.f)) * gs;
+      float e0 = ex2_fast(fmaf(f.x, kLog2e, -m2)), e1 = ex2_fast(fmaf(f.y, kLog2e, -m2));
       if (v >= vlast) {
-        if (c >= V_real) g0 = 0.f;
-        if (c + 1 >= V_real) g1 = 0.f;
+        const int c = v * 8 + 2 * j;
+        if (c >= V_real) e0 = 0.f;
+        if (c + 1 >= V_real) e1 = 0.f;
       }
-      w[j] = pack_bf16x2(g0, g1);
+      s += e0 + e1;
+      w[j] = pack_bf16x2(e0, e1);
     }
+    if (write_grad) sw[v] = u;
+  }
+  s = cta_reduce<false>(s, sh);
+  const float lse = m + __logf(s);
+  if (threadIdx.x == 0 && losses != nullptr) losses[row] = ignored ? 0.f : lse - tgt_logit;
+  if (!write_grad) return;
+  // ---- gradient, in place: e * (grad_scale / sum) - onehot * grad_scale
+  // (cta_reduce ended with a barrier after every thread's writes above)
+  const float gs = ignored ? 0.f : grad_scale;
+  const float k = gs / s;
+  const int vt = ignored ? -1 : (int)(tgt >> 3), jt = (int)(tgt & 7);
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) {
+    uint4 u = sw[v];
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 e = unpack_bf16x2(w[j]);
+      g[2 * j] = e.x * k;
+      g[2 * j + 1] = e.y * k;
+    }
+    if (v == vt) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j == jt) g[j] -= gs;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(g[2 * j], g[2 * j + 1]);
     sw[v] = u;
   }
   fence_proxy_async();  // make the generic-proxy writes visible to the bulk copy
@@ -165,6 +176,8 @@ __global__ void __launch_bounds__(kThreads)
 ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ targets,
                   float* __restrict__ losses, int V_real, int V_pad, long long ld, float grad_scale,
                   int write_grad, int ignore_index) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sm[kThreads / 32], ss[kThreads / 32];
   __shared__ float row_max, row_lse;
   const int row = blockIdx.x;
@@ -244,6 +257,8 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const IdxT* __restrict__ t
 // Sum of n floats into *out (scaled); single CTA, fixed order.
 __global__ void reduce_sum_kernel(const float* __restrict__ x, int n, float scale, float* out,
                                   int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32];
   float s = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
@@ -278,29 +293,29 @@ int ce_fwd_bwd(void* logits, const void* targets, int idx_is_64, float* losses, 
       attr_set = true;
     }
     if (idx_is_64)
-      ce_row_in_smem_kernel<long long><<<M, kRowThreads, row_bytes, stream>>>(
+      launch_kernel(ce_row_in_smem_kernel<long long>, dim3(M), dim3(kRowThreads), row_bytes, stream, true, 
           (__nv_bfloat16*)logits, (const long long*)targets, losses, V_real, V_pad, ld, grad_scale,
           write_grad, ignore_index, nullptr);
     else
-      ce_row_in_smem_kernel<int><<<M, kRowThreads, row_bytes, stream>>>(
+      launch_kernel(ce_row_in_smem_kernel<int>, dim3(M), dim3(kRowThreads), row_bytes, stream, true, 
           (__nv_bfloat16*)logits, (const int*)targets, losses, V_real, V_pad, ld, grad_scale, write_grad,
           ignore_index, nullptr);
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
   }
   if (idx_is_64)
-    ce_fwd_bwd_kernel<long long><<<M, kThreads, 0, stream>>>((__nv_bfloat16*)logits,
+    launch_kernel(ce_fwd_bwd_kernel<long long>, dim3(M), dim3(kThreads), 0, stream, true, (__nv_bfloat16*)logits,
                                                             (const long long*)targets, losses, V_real,
                                                             V_pad, ld, grad_scale, write_grad,
                                                             ignore_index);
   else
-    ce_fwd_bwd_kernel<int><<<M, kThreads, 0, stream>>>((__nv_bfloat16*)logits, (const int*)targets,
+    launch_kernel(ce_fwd_bwd_kernel<int>, dim3(M), dim3(kThreads), 0, stream, true, (__nv_bfloat16*)logits, (const int*)targets,
                                                       losses, V_real, V_pad, ld, grad_scale,
                                                       write_grad, ignore_index);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
 int reduce_sum(const float* x, int n, float scale, float* out, int accumulate, cudaStream_t stream) {
-  reduce_sum_kernel<<<1, 1024, 0, stream>>>(x, n, scale, out, accumulate);
+  launch_kernel(reduce_sum_kernel, dim3(1), dim3(1024), 0, stream, true, x, n, scale, out, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

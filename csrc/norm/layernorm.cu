@@ -12,6 +12,7 @@
 // Semantics follow nn.LayerNorm(bias=False) of the reference model (nn/gpt2/modules.py:62-69,81)
 // and the hand-written weight+bias LayerNorm of the char-level model (nn/gpt/3_gpt.py:79-91):
 // biased variance, eps inside the square root.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "norm.h"
 
@@ -46,6 +47,8 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
                      const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
                      float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int C,
                      float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarpsPerCta + warp;
   if (row >= M) return;
@@ -106,6 +109,8 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dresid,
                      __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, int M, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sh[];  // [kWarpsPerCta][2][C]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float dw_acc[NVEC][8];
@@ -226,6 +231,8 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 __global__ void __launch_bounds__(1024)
 layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int num_partials,
                             float* __restrict__ dw, float* __restrict__ db, int C, int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32][33];
   const int col_in = threadIdx.x & 31, part = threadIdx.x >> 5;
   const int c2 = blockIdx.x * 32 + col_in;  // column of the [2C] partial row
@@ -257,7 +264,7 @@ int layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* m
   if (M <= 0) return 0;
   const int grid = (M + kWarpsPerCta - 1) / kWarpsPerCta;
 #define Z2H_LN_FWD(NV)                                                                         \
-  layernorm_fwd_kernel<NV><<<grid, kWarpsPerCta * 32, 0, stream>>>(                             \
+  launch_kernel(layernorm_fwd_kernel<NV>, dim3(grid), dim3(kWarpsPerCta * 32), 0, stream, true,                              \
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, \
       mean, rstd, M, C, eps)
   if (C <= 768) Z2H_LN_FWD(3);
@@ -283,7 +290,7 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
                            kWarpsPerCta * 2 * 32 * 8 * NV * (int)sizeof(float));               \
       attr = true;                                                                             \
     }                                                                                          \
-    kern<<<grid, kWarpsPerCta * 32, smem, stream>>>(                                           \
+    launch_kernel(kern, dim3(grid), dim3(kWarpsPerCta * 32), smem, stream, true,                                            \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, rstd, \
         (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, M, C);                      \
   } while (0)
@@ -292,7 +299,7 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
   else if (C <= 1024) { if (has_db) Z2H_LN_BWD(4, true); else Z2H_LN_BWD(4, false); }
   else { if (has_db) Z2H_LN_BWD(8, true); else Z2H_LN_BWD(8, false); }
 #undef Z2H_LN_BWD
-  layernorm_bwd_reduce_kernel<<<(2 * C + 31) / 32, 1024, 0, stream>>>(scratch, grid, dw, db, C,
+  launch_kernel(layernorm_bwd_reduce_kernel, dim3((2 * C + 31) / 32), dim3(1024), 0, stream, true, scratch, grid, dw, db, C,
                                                                     accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

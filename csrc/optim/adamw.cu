@@ -4,6 +4,7 @@
 // Replaces torch.nn.utils.clip_grad_norm_ + torch.optim.AdamW(fused=True) of the reference
 // trainers (nn/gpt2/train.py:73-84,126-127, nn/gpt2/train_ddp.py:92-103,142-143): the update
 // rule, the eps placement and the decoupled weight decay match torch's AdamW.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "optim.h"
 #include "adamw_update.cuh"
@@ -89,6 +90,8 @@ adamw_step_kernel(float* __restrict__ p32, float* __restrict__ g, float* __restr
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ dy, int M, int N, long long ld,
                    float* __restrict__ db, int rows_per_slab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[8][256];
   const int cv = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int c = blockIdx.x * 256 + cv * 8;
@@ -173,7 +176,7 @@ int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accum
   if (slabs < 1) slabs = 1;
   const int rows_per_slab = (M + slabs - 1) / slabs;
   dim3 grid((N + 255) / 256, slabs);
-  colsum_bf16_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, M, N, ld, db, rows_per_slab);
+  launch_kernel(colsum_bf16_kernel, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)dy, M, N, ld, db, rows_per_slab);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
