@@ -147,7 +147,8 @@ def build_ours(rank, world, local):
     comm = None
     if world > 1:
         from zero_to_hero_b200.parallel.fused_ddp import FusedDDP
-        comm = FusedDDP(torch.device("cuda", local))
+        # Z2H_NVLS=1 selects the multimem flavour of the fused reduce-scatter + AdamW + all-gather
+        comm = FusedDDP(torch.device("cuda", local), nvls=os.environ.get("Z2H_NVLS", "0") == "1")
     eng = GPT2TrainEngine(cfg, device=torch.device("cuda", local), comm=comm)
     micro = TOTAL_TOKENS // (MICRO_B * SEQ * world)
 

@@ -14,6 +14,12 @@
 //                          also clears the local gradient buffer for the next step
 //   finish                 wait until every peer has finished writing, bump the epoch
 //
+// NVLS flavour (FusedStepArgs::grads_mc / p16_mc set): the same three launches and signalling,
+// but the reduce-scatter reads each 16 bytes of the shard once through the multicast address with
+// multimem.ld_reduce (the NVSwitch adds the ranks' copies in fp32) and the all-gather is one
+// multimem.st per 16 bytes (the switch replicates the store), so every byte crosses this GPU's
+// links once instead of once per peer.
+//
 // This replaces DistributedDataParallel's bucketed NCCL all-reduce + clip_grad_norm_ + fused
 // AdamW of the reference trainer (nn/gpt2/train_ddp.py:89,141-143). A one-shot variant for
 // small models (every rank reduces everything and updates a replicated state) and standalone
@@ -100,10 +106,28 @@ enum SlotKind : int {
 // -------------------------------------------------------------------------------------------
 // two-shot fused step
 // -------------------------------------------------------------------------------------------
+// in-switch reduction: the sum over all ranks of the 16 bytes at a multicast address
+__device__ __forceinline__ float4 multimem_ld_reduce_add_f32x4(const void* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+// in-switch broadcast: 16 bytes stored to every rank's copy behind a multicast address
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+template <bool NVLS>
 __global__ void __launch_bounds__(kThreads)
-reduce_scatter_sumsq_kernel(Peers grads, Peers pads, int rank, int world, long long shard_off,
-                            long long shard_n, float* partials, const uint32_t* epoch_ptr,
-                            uint64_t budget_ns, int* status) {
+reduce_scatter_sumsq_kernel(Peers grads, const float* grads_mc, Peers pads, int rank, int world,
+                            long long shard_off, long long shard_n, float* partials,
+                            const uint32_t* epoch_ptr, uint64_t budget_ns, int* status) {
   __shared__ int failed;
   __shared__ float sh[kThreads / 32];
   const uint32_t epoch = *epoch_ptr + 1;
@@ -118,12 +142,16 @@ reduce_scatter_sumsq_kernel(Peers grads, Peers pads, int rank, int world, long l
   for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * kThreads) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    // start at the next rank so that the ranks do not all pull from the same peer at once
-    for (int k = 1; k <= world; ++k) {
-      const int r = (rank + k) % world;
-      const float4 x = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.ptr[r]) +
-                                                       shard_off)[i];
-      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    if (NVLS) {
+      acc = multimem_ld_reduce_add_f32x4(reinterpret_cast<const float4*>(grads_mc + shard_off) + i);
+    } else {
+      // start at the next rank so that the ranks do not all pull from the same peer at once
+      for (int k = 1; k <= world; ++k) {
+        const int r = (rank + k) % world;
+        const float4 x = reinterpret_cast<const float4*>(
+            reinterpret_cast<const float*>(grads.ptr[r]) + shard_off)[i];
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      }
     }
     reinterpret_cast<float4*>(mine)[i] = acc;
     sumsq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
@@ -132,8 +160,9 @@ reduce_scatter_sumsq_kernel(Peers grads, Peers pads, int rank, int world, long l
   if (threadIdx.x == 0) partials[blockIdx.x] = sumsq;
 }
 
+template <bool NVLS>
 __global__ void __launch_bounds__(kThreads)
-norm_adamw_allgather_kernel(Peers p16, Peers pads, float* g_local, float* p32, float* m, float* v,
+norm_adamw_allgather_kernel(Peers p16, __nv_bfloat16* p16_mc, Peers pads, float* g_local, float* p32, float* m, float* v,
                             int rank, int world, long long shard_off, long long shard_n,
                             long long total_n, long long n_decay, const float* hyper,
                             const float* partials, int num_partials, float* norm_out,
@@ -206,9 +235,13 @@ norm_adamw_allgather_kernel(Peers p16, Peers pads, float* g_local, float* p32, f
     uint4 o;
     o.x = pack_bf16x2(pv[0], pv[1]); o.y = pack_bf16x2(pv[2], pv[3]);
     o.z = pack_bf16x2(pv[4], pv[5]); o.w = pack_bf16x2(pv[6], pv[7]);
-    for (int kk = 0; kk < world; ++kk) {
-      const int r = (rank + kk) % world;
-      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p16.ptr[r]) + shard_off)[i] = o;
+    if (NVLS) {
+      multimem_st_b128(reinterpret_cast<uint4*>(p16_mc + shard_off) + i, o);
+    } else {
+      for (int kk = 0; kk < world; ++kk) {
+        const int r = (rank + kk) % world;
+        reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p16.ptr[r]) + shard_off)[i] = o;
+      }
     }
   }
   // last CTA out tells every peer that this rank's writes are complete
@@ -406,14 +439,26 @@ int fused_step_twoshot(const FusedStepArgs& a, cudaStream_t stream) {
   const Peers p16 = to_peers(a.p16, a.world);
   const Peers pads = to_peers(a.pads, a.world);
   const int grid_a = grid_for(a.shard_n / 4, a.max_ctas > 0 ? a.max_ctas : 296);
-  reduce_scatter_sumsq_kernel<<<grid_a, kThreads, 0, stream>>>(
-      grads, pads, a.rank, a.world, a.shard_off, a.shard_n, a.partials, a.epoch, a.budget_ns,
-      a.status);
+  const bool nvls = a.grads_mc != nullptr && a.p16_mc != nullptr;
+  if (nvls)
+    reduce_scatter_sumsq_kernel<true><<<grid_a, kThreads, 0, stream>>>(
+        grads, reinterpret_cast<const float*>(a.grads_mc), pads, a.rank, a.world, a.shard_off, a.shard_n,
+        a.partials, a.epoch, a.budget_ns, a.status);
+  else
+    reduce_scatter_sumsq_kernel<false><<<grid_a, kThreads, 0, stream>>>(
+        grads, nullptr, pads, a.rank, a.world, a.shard_off, a.shard_n, a.partials, a.epoch, a.budget_ns,
+        a.status);
   const int grid_b = grid_for(a.total_n / 4, a.max_ctas > 0 ? a.max_ctas : 296);
-  norm_adamw_allgather_kernel<<<grid_b, kThreads, 0, stream>>>(
-      p16, pads, reinterpret_cast<float*>(a.grads[a.rank]), a.p32, a.m, a.v, a.rank, a.world,
-      a.shard_off, a.shard_n, a.total_n, a.n_decay, a.hyper, a.partials, grid_a, a.norm_out, a.epoch,
-      a.done_counter, a.budget_ns, a.status);
+  if (nvls)
+    norm_adamw_allgather_kernel<true><<<grid_b, kThreads, 0, stream>>>(
+        p16, reinterpret_cast<__nv_bfloat16*>(a.p16_mc), pads, reinterpret_cast<float*>(a.grads[a.rank]),
+        a.p32, a.m, a.v, a.rank, a.world, a.shard_off, a.shard_n, a.total_n, a.n_decay, a.hyper,
+        a.partials, grid_a, a.norm_out, a.epoch, a.done_counter, a.budget_ns, a.status);
+  else
+    norm_adamw_allgather_kernel<false><<<grid_b, kThreads, 0, stream>>>(
+        p16, nullptr, pads, reinterpret_cast<float*>(a.grads[a.rank]), a.p32, a.m, a.v, a.rank, a.world,
+        a.shard_off, a.shard_n, a.total_n, a.n_decay, a.hyper, a.partials, grid_a, a.norm_out, a.epoch,
+        a.done_counter, a.budget_ns, a.status);
   finish_kernel<<<1, 32, 0, stream>>>(pads, a.rank, a.world, a.epoch, kSlotDone, a.budget_ns,
                                       a.status);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
@@ -484,6 +529,26 @@ int z2h_fused_step_twoshot(void* const* grads, void* const* p16, void* const* pa
   a.hyper = hyper; a.partials = partials; a.norm_out = norm_out;
   a.epoch = epoch; a.done_counter = done_counter; a.budget_ns = budget_ns; a.status = status;
   a.max_ctas = max_ctas;
+  a.grads_mc = nullptr;
+  a.p16_mc = nullptr;
+  return z2h::fused_step_twoshot(a, (cudaStream_t)stream);
+}
+int z2h_fused_step_twoshot_nvls(void* const* grads, void* const* p16, void* const* pads, void* grads_mc,
+                                void* p16_mc, float* p32, float* m, float* v, int rank, int world,
+                                long long shard_off, long long shard_n, long long total_n,
+                                long long n_decay, const float* hyper, float* partials, float* norm_out,
+                                unsigned int* epoch, unsigned int* done_counter,
+                                unsigned long long budget_ns, int* status, int max_ctas, void* stream) {
+  z2h::FusedStepArgs a;
+  a.grads = grads; a.p16 = p16; a.pads = pads;
+  a.p32 = p32; a.m = m; a.v = v;
+  a.rank = rank; a.world = world;
+  a.shard_off = shard_off; a.shard_n = shard_n; a.total_n = total_n; a.n_decay = n_decay;
+  a.hyper = hyper; a.partials = partials; a.norm_out = norm_out;
+  a.epoch = epoch; a.done_counter = done_counter; a.budget_ns = budget_ns; a.status = status;
+  a.max_ctas = max_ctas;
+  a.grads_mc = grads_mc;
+  a.p16_mc = p16_mc;
   return z2h::fused_step_twoshot(a, (cudaStream_t)stream);
 }
 int z2h_allreduce(void* const* bufs, void* const* pads, void* out, int rank, int world, long long n,

@@ -31,6 +31,12 @@ struct FusedStepArgs {
   uint64_t budget_ns;            // time budget of every cross-rank wait
   int* status;                   // device status word
   int max_ctas;                  // 0 = default
+  // NVLS flavour: multicast addresses of the gradient and bf16 parameter buffers (the same
+  // symmetric allocations seen through the NVSwitch multicast object), or null for plain peer
+  // loads / stores. With them the reduce-scatter is one multimem.ld_reduce per 16 bytes (the
+  // switch adds the ranks' copies) and the all-gather one multimem.st (the switch replicates it).
+  void* grads_mc;
+  void* p16_mc;
 };
 
 // Reduce-scatter + global-norm clip + AdamW on the shard + all-gather of bf16 parameters.

@@ -82,6 +82,38 @@ def main():
         assert torch.equal(w, ref), "bf16 replicas differ"
     if rank == 0:
         print("fused ddp OK", flush=True)
+
+    # ---- multimem (NVLS) flavour of the same step, where the system gives a multicast address
+    probe = FusedDDP(dev, nvls=True)
+    probe.setup(1 << 16, 1 << 16)
+    have_nvls = torch.tensor([int(probe.nvls)], device=dev)
+    dist.all_reduce(have_nvls, op=dist.ReduceOp.MIN)
+    del probe
+    if have_nvls.item() == 1:
+        e_nvls = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, nvls=True), seed=7)
+        e_p2p = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev), seed=7)
+        assert e_nvls.comm.nvls and not e_p2p.comm.nvls
+        g2 = torch.Generator().manual_seed(2000 + rank)
+        for step in range(3):
+            batches = []
+            for _ in range(2):
+                tok = torch.randint(0, 512, (2 * 128 + 1,), generator=g2)
+                batches.append((tok[:-1].view(2, 128).pin_memory(), tok[1:].view(2, 128).pin_memory()))
+            for e in (e_nvls, e_p2p):
+                e.train_step(batches, lr=1e-3)
+            _lib.check_status(dev)
+            assert abs(e_nvls.read_loss() - e_p2p.read_loss()) < 1e-3
+            assert abs(e_nvls.read_grad_norm() - e_p2p.read_grad_norm()) / e_p2p.read_grad_norm() < 1e-3
+            a, b = e_nvls.full_master(), e_p2p.full_master()
+            assert (a - b).abs().mean().item() / b.abs().mean().item() < 1e-4
+            w = e_nvls.p16.float()
+            ref = w.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(w, ref), "bf16 replicas differ (NVLS)"
+        if rank == 0:
+            print("fused ddp NVLS OK", flush=True)
+    elif rank == 0:
+        print("no multicast address: NVLS flavour not exercised", flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

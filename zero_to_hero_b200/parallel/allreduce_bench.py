@@ -10,7 +10,8 @@ with CUDA events and as the maximum over ranks:
 and, for the fp32 sizes, the whole optimizer step of a flat parameter vector of that many
 gradients:
   * fused: reduce-scatter + clip + AdamW on the owned shard + all-gather of the bf16 weights
-    (`FusedDDP.fused_step`, three launches, no library call),
+    (`FusedDDP.fused_step`, three launches, no library call), with plain peer loads / stores and,
+    where the system provides a multicast address, with multimem (NVLS) instructions,
   * baseline: NCCL all-reduce followed by the single-GPU norm + AdamW kernels on every rank.
 Bus bandwidth is the usual 2 (n-1)/n * bytes / time. One JSON line per measurement on rank 0.
 The waits inside the kernels are bounded; a rank that does not show up ends them with a status
@@ -106,12 +107,20 @@ def main():
             if nbytes < (1 << 16) or nbytes > (1 << 30):
                 continue
             n = nbytes // 4 // (8 * world) * (8 * world)
-            fused = FusedDDP(dev)
-            fused.setup(n, n)
-            fused.g.normal_(std=0.01)
-            fused.load_master(torch.zeros(n, device=dev))
             iters = a.iters if nbytes <= (64 << 20) else max(3, a.iters // 4)
-            ms_f = _time(lambda: fused.fused_step(hyper, norm), iters, a.warmup, group)
+            ms_flavour = {}
+            for nvls in (False, True):
+                fused = FusedDDP(dev, nvls=nvls)
+                fused.setup(n, n)
+                if nvls and not fused.nvls:  # no multicast address on this system
+                    del fused
+                    continue
+                fused.g.normal_(std=0.01)
+                fused.load_master(torch.zeros(n, device=dev))
+                ms_flavour[nvls] = _time(lambda: fused.fused_step(hyper, norm), iters, a.warmup, group)
+                del fused
+                torch.cuda.empty_cache()
+            ms_f = ms_flavour[False]
             # baseline: library all-reduce, then the single-GPU norm + AdamW kernels, replicated
             g = torch.randn(n, device=dev) * 0.01
             p32, m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
@@ -126,8 +135,9 @@ def main():
             ms_b = _time(baseline, iters, a.warmup, group)
             _lib.check_status(dev)
             emit(op="allreduce+adamw", grad_bytes=n * 4, world=world, fused_us=round(ms_f * 1e3, 2),
+                 fused_nvls_us=round(ms_flavour[True] * 1e3, 2) if True in ms_flavour else None,
                  nccl_plus_adamw_us=round(ms_b * 1e3, 2), speedup=round(ms_b / ms_f, 3))
-            del fused, g, p32, m, v, p16
+            del g, p32, m, v, p16
             torch.cuda.empty_cache()
     dist.barrier(group)
     dist.destroy_process_group()

@@ -114,12 +114,21 @@ class FusedDDP(PeerComm):
 
     launches_per_step = 3
 
-    def __init__(self, device: torch.device, group=None, budget_s: float = 2.0):
+    def __init__(self, device: torch.device, group=None, budget_s: float = 2.0, nvls: bool = False):
+        """`nvls=True` asks for the multimem flavour (in-switch reduction and broadcast); it is
+        used when the symmetric allocations come with a multicast address, otherwise the plain
+        peer load / store kernels run (`self.nvls` tells which)."""
         super().__init__(device, group, budget_s)
         self._step = _lib_fn("z2h_fused_step_twoshot", [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong,
             c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
             c_ulonglong, c_void_p, c_int, c_void_p])
+        self._step_nvls = _lib_fn("z2h_fused_step_twoshot_nvls", [
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+            c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_ulonglong, c_void_p, c_int, c_void_p])
+        self._want_nvls = nvls
+        self.nvls = False
         self._first = True
 
     def setup(self, total: int, n_decay: int) -> None:
@@ -129,6 +138,7 @@ class FusedDDP(PeerComm):
         self.p16_buf = SymmetricBuffer(total, torch.bfloat16, dev, self.group)
         self.g, self.p16 = self.g_buf.tensor, self.p16_buf.tensor
         self.shard_off, self.shard_n = shard_bounds(total, self.world_size, self.rank)
+        self.nvls = bool(self._want_nvls and self.g_buf.multicast_ptr and self.p16_buf.multicast_ptr)
         n = max(self.shard_n, 8)
         self.p32_shard = torch.zeros(n, device=dev)
         self.m_shard = torch.zeros(n, device=dev)
@@ -160,6 +170,18 @@ class FusedDDP(PeerComm):
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
             self._first = False
+        if self.nvls:
+            rc = self._step_nvls(_ptr_array(self.g_buf.ptrs), _ptr_array(self.p16_buf.ptrs),
+                                 _ptr_array(self.pad.ptrs), self.g_buf.multicast_ptr,
+                                 self.p16_buf.multicast_ptr, _lib.ptr(self.p32_shard),
+                                 _lib.ptr(self.m_shard), _lib.ptr(self.v_shard), self.rank,
+                                 self.world_size, self.shard_off, self.shard_n, self.total, self.n_decay,
+                                 _lib.ptr(hyper), _lib.ptr(self.partials), _lib.ptr(norm_out),
+                                 _lib.ptr(self.epoch), _lib.ptr(self.done_counter), self.budget_ns,
+                                 _lib.ptr(_lib.status_word(self.device)), 0, _lib.stream_ptr())
+            if rc != 0:
+                raise RuntimeError(f"z2h_fused_step_twoshot_nvls failed with code {rc}")
+            return
         rc = self._step(_ptr_array(self.g_buf.ptrs), _ptr_array(self.p16_buf.ptrs),
                         _ptr_array(self.pad.ptrs), _lib.ptr(self.p32_shard), _lib.ptr(self.m_shard),
                         _lib.ptr(self.v_shard), self.rank, self.world_size, self.shard_off,

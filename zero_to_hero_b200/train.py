@@ -86,7 +86,7 @@ def train(cfg: Config, resume: str = "") -> dict:
         comm = None
         if world > 1:
             from .parallel.fused_ddp import FusedDDP, TorchDDPComm
-            comm = FusedDDP(device) if cfg.dist.fused_allreduce else TorchDDPComm(device)
+            comm = FusedDDP(device, nvls=cfg.dist.nvls) if cfg.dist.fused_allreduce else TorchDDPComm(device)
         eng = GPT2TrainEngine(cfg, device, comm=comm)
         start = 0
         if resume:
