@@ -23,6 +23,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
+#include "../common/trace.cuh"
 #include "../common/dropout.cuh"
 #include <cstdlib>
 
@@ -126,11 +127,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
       tma_load_2d(sK, &tm_qkv, kv_full, p.C + h * HD, row0 + j * TS);
       tma_load_2d(sV, &tm_qkv, kv_full, 2 * p.C + h * HD, row0 + j * TS);
+      Z2H_TRACE_DECL(0)
+      Z2H_TRACE();
       for (int it = 0; it < n_iter; ++it) {
         const int i = j + it;
         const int s = it % Q_STAGES;
         const uint32_t ph = (it / Q_STAGES) & 1;
         if (!mbar_wait_bounded(&qdo_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
+        Z2H_TRACE();
         mbar_arrive_expect_tx(&qdo_full[s], 2 * TILE_BYTES + 2 * TS * 4);
         tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &qdo_full[s], h * HD, row0 + i * TS);
         tma_load_2d(sdO + s * TILE_BYTES, &tm_do, &qdo_full[s], h * HD, row0 + i * TS);
@@ -174,12 +178,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
                         idesc_st, k > 0);
         tc_commit(st_full);
       };
+      Z2H_TRACE_DECL(1)
+      Z2H_TRACE();
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFull);
       if (ok) ok = mbar_wait_bounded(&qdo_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      Z2H_TRACE();
       if (ok) {
         tc_fence_after();
         issue_st(0);
       }
+      Z2H_TRACE();
       // Software pipeline: as soon as P^T / dS^T of tile `it` are in shared memory, S^T / dP^T of
       // tile it+1 are issued first (their TMEM columns were just drained), then the three
       // products that consume tile `it`; the compute warps meanwhile read dQ of tile it-1 and
@@ -188,6 +196,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         const int s = it % Q_STAGES;
         const uint32_t pb = (it & 1) * PT_BYTES;
         if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        Z2H_TRACE();
         if (it + 1 < n_iter) {
           const int s2 = (it + 1) % Q_STAGES;
           const uint32_t ph2 = ((it + 1) / Q_STAGES) & 1;
@@ -195,6 +204,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           tc_fence_after();
           issue_st(s2);
         }
+        Z2H_TRACE();
         tc_fence_after();
         const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
         const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
@@ -210,13 +220,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
                         idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
         }
+        // dV and dK were the last readers of this Q / dO stage: hand it back before the dQ product
+        tc_commit(&qdo_empty[s]);
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
           tc_mma_f16_ss(tmem_base + DQ_COL + (it & 1) * HD, desc_advance(dst_mn_desc, pb + k * 2048),
                         desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
         }
         tc_commit(dq_full);
-        tc_commit(&qdo_empty[s]);
+        Z2H_TRACE();
       }
     }
   } else {
@@ -253,6 +265,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     const unsigned long long drop_wpr = (unsigned long long)((p.T + 3) / 4);  // mask words per query row
     const int drop_byte = (j * TS + r) & 3;
     bool ok = true;
+    Z2H_TRACE_DECL(2)
+#define Z2H_CTRACE()                      \
+  do {                                    \
+    if (warp == 2 && lane == 0) Z2H_TRACE(); \
+  } while (0)
+    Z2H_CTRACE();
     for (int it = 0; it < n_iter; ++it) {
       const int i = j + it;
       const int s = it % Q_STAGES;
@@ -261,11 +279,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         ok = false;
         break;
       }
+      Z2H_CTRACE();  // Q / dO tile and statistics are there
       if (!mbar_wait_bounded(st_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      Z2H_CTRACE();  // scores are there
       const uint32_t pb = (it & 1) * PT_BYTES;  // which P^T / dS^T buffer this tile uses
       // mask word of (first query of tile i, this thread's key); one row of words per query
       const unsigned long long drop_q0 =
@@ -282,6 +302,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64 + 32, sv[1]);
       tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64 + 32, dv[1]);
       tmem_ld_wait();
+      Z2H_CTRACE();  // scores in registers
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
@@ -337,6 +358,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
                        : "memory");
         }
       }
+      Z2H_CTRACE();  // P^T / dS^T written
       // The products of tile it-1 must have completed before this warp signals tile `it`: a later
       // wait could otherwise see the barrier two phases ahead and mistake the parity.
       if (it > 0 && !mbar_wait_bounded(dq_full, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
@@ -347,8 +369,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);  // one arrival per compute warp
+      Z2H_CTRACE();  // arrived
       // while the tensor cores work on this tile, fold dQ of the previous one into global memory
       if (it > 0) drain_dq(it - 1);
+      Z2H_CTRACE();  // dQ of the previous tile drained
     }
     if (ok && n_iter > 0) {
       ok = mbar_wait_bounded(dq_full, (n_iter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
@@ -546,3 +570,9 @@ extern "C" int z2h_flash_bwd(const void* qkv, const void* out, const void* dout,
   return z2h::flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, status,
                         (cudaStream_t)stream);
 }
+
+#ifdef Z2H_KERNEL_TRACE
+extern "C" int z2h_flash_bwd_trace_read(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_kernel_trace, sizeof(g_kernel_trace));
+}
+#endif

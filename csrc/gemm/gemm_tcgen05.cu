@@ -25,7 +25,7 @@
 #include "../common/tma_desc.h"
 #include "gemm.h"
 
-#include "gemm_trace.cuh"
+#include "../common/trace.cuh"
 
 #include "gemm_epilogue.cuh"
 
@@ -70,9 +70,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   pdl_launch_dependents();
-#ifdef Z2H_GEMM_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 64) g_epi_n = 0;
-#endif
 
   // every role walks the same sequence of work segments
   gemm_detail::TileScheduler sched(p, BM, BN, BK, blockIdx.x, gridDim.x);
@@ -324,9 +321,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace z2h
 
-#ifdef Z2H_GEMM_TRACE
+#ifdef Z2H_KERNEL_TRACE
 extern "C" int z2h_gemm_trace_read(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
+  return (int)cudaMemcpyFromSymbol(host_out, g_kernel_trace, sizeof(g_kernel_trace));
 }
 #endif
 extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }

@@ -17,7 +17,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "gemm.h"
-#include "gemm_trace.cuh"
+#include "../common/trace.cuh"
 #include "gemm_epilogue.cuh"
 
 namespace z2h {
@@ -305,8 +305,8 @@ int gemm_bf16_pair(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace z2h
 
-#ifdef Z2H_GEMM_TRACE
+#ifdef Z2H_KERNEL_TRACE
 extern "C" int z2h_gemm_trace_read_pair(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
+  return (int)cudaMemcpyFromSymbol(host_out, g_kernel_trace, sizeof(g_kernel_trace));
 }
 #endif
