@@ -144,6 +144,8 @@ def build_ours(rank, world, local):
         setattr(cfg.model, k, v)
     cfg.train.micro_batch = MICRO_B
     cfg.train.total_batch_tokens = TOTAL_TOKENS
+    if "Z2H_OVERLAP" in os.environ:  # A/B switch for the two-stream backward schedule
+        cfg.train.overlap_wgrad = os.environ["Z2H_OVERLAP"] == "1"
     comm = None
     if world > 1:
         from zero_to_hero_b200.parallel.fused_ddp import FusedDDP

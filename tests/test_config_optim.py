@@ -53,3 +53,23 @@ def test_param_groups_dim_rule():
     assert n == sum(p.numel() for p in model.parameters())  # tied weight counted once
     opt = build_optimizer(model, cfg.optim)
     assert opt.param_groups[0]["betas"] == (0.9, 0.95)
+
+
+def test_pick_split_k_fills_whole_waves():
+    """Split-K factors for the weight-gradient shapes of GPT-2 124M at 16,384 tokens: the factor
+    must keep the 74 CTA pairs busy for whole waves, and huge outputs need no split."""
+    import math
+    from zero_to_hero_b200.ops.functional import pick_split_k
+
+    def tiles(n_out, k_in):
+        return math.ceil(n_out / 128) * math.ceil(k_in / 256)
+
+    kb = 16384 // 64
+    for n_out, k_in in ((2304, 768), (768, 768), (3072, 768), (768, 3072)):
+        s = pick_split_k(tiles(n_out, k_in), kb)
+        pair_tiles = math.ceil(tiles(n_out, k_in) / 2)
+        waves = pair_tiles * s / 74
+        assert s >= 1 and kb // s >= 16
+        assert math.ceil(waves) - waves < 0.15, (n_out, k_in, s, waves)
+    assert pick_split_k(tiles(50304, 768), kb) == 1
+    assert pick_split_k(4, 8) == 1  # K too short to split

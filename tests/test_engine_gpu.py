@@ -23,8 +23,8 @@ def _batches(g, n=2):
     return out
 
 
-@pytest.mark.parametrize("graph", [False, True])
-def test_engine_tracks_fp32_reference_training(graph):
+@pytest.mark.parametrize("graph,overlap", [(False, False), (True, False), (False, True), (True, True)])
+def test_engine_tracks_fp32_reference_training(graph, overlap):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from zero_to_hero_b200.engine import GPT2TrainEngine
@@ -34,6 +34,7 @@ def test_engine_tracks_fp32_reference_training(graph):
 
     cfg = _cfg()
     cfg.train.use_cuda_graph = graph
+    cfg.train.overlap_wgrad = overlap  # weight gradients on a second stream
     eng = GPT2TrainEngine(cfg, "cuda", seed=1)
     ref = GPT2(cfg.model).float()
     ref.load_state_dict({k: v.cpu() for k, v in eng.state_dict().items()})

@@ -149,6 +149,9 @@ class GPT2TrainEngine:
         self.opt_step = 0
         self.seed_value = cfg.train.seed if seed is None else seed
         self._alloc_activations(cfg.train.micro_batch, mc.block_size)
+        self._side = torch.cuda.Stream(device=self.device)
+        self._side_done = []
+        self._overlap = False
         self._graph = None
         self._graph_scale = None
         self.launches_per_micro_step = 0
@@ -243,6 +246,7 @@ class GPT2TrainEngine:
         self.losses = buf(M, dtype=f32)
         # backward scratch
         self.d_resid = buf(M, C)
+        self.d_resid_alt = buf(M, C)  # second residual-gradient buffer for the two-stream schedule
         self.d_c = buf(M, C)
         # dropout (the reference trains with 0.2): masks are a function of (seed, site, index),
         # the seed lives on the device so that a captured graph sees a new one at every replay
@@ -271,6 +275,30 @@ class GPT2TrainEngine:
         else:
             G.gemm(dy, x, out, a_mn=True, b_mn=True, epi=G.EPI_ATOMIC_ADD, split_k=sk)
         self._n += 1
+
+    # Two-stream schedule of the backward pass: the weight-gradient GEMMs and bias column sums of
+    # a sub-layer do not feed the data-gradient chain, so they can run on a side stream and fill
+    # the SMs that the chain's kernels leave idle in their last partial wave. A side group may lag
+    # the chain by one sub-layer; the residual gradient alternates between two buffers so that the
+    # chain never overwrites what a lagging group still reads.
+    def _on_side(self, fn) -> None:
+        if not self._overlap:
+            fn()
+            return
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(ready)
+            fn()
+            done = torch.cuda.Event()
+            done.record(self._side)
+        self._side_done.append(done)
+
+    def _join_side(self, keep_last: int = 0) -> None:
+        main = torch.cuda.current_stream()
+        while len(self._side_done) > keep_last:
+            main.wait_event(self._side_done.pop(0))
 
     def _forward_backward(self, grad_scale: float, loss_scale: float) -> None:
         """One micro-step on the static buffers `idx` / `tgt` (all launches, no host sync)."""
@@ -337,8 +365,12 @@ class GPT2TrainEngine:
         G.gemm(logits_v, w("transformer.wte.weight"), self.d_c, b_mn=True)
         self._n += 1
         self._wgrad(logits_v, self.xf, "transformer.wte.weight")
+        self._overlap = bool(self.cfg.train.overlap_wgrad) and pd == 0.0
+        self._side_done = []
+        R = [self.d_resid, self.d_resid_alt if self._overlap else self.d_resid]
+        cur = 0  # R[cur] holds the residual-stream gradient
         N.layernorm_bwd(self.d_c, self.resid[L], w("transformer.ln_f.weight"), self.stats_f[0],
-                        self.stats_f[1], None, self.d_resid, gw("transformer.ln_f.weight"),
+                        self.stats_f[1], None, R[cur], gw("transformer.ln_f.weight"),
                         glnb("transformer.ln_f.bias"), self.ln_scratch)
         self._n += 2
         for l in reversed(range(L)):
@@ -346,43 +378,64 @@ class GPT2TrainEngine:
             st = self.stats[l]
             # MLP (the gradient of the projection output is the residual gradient through the
             # dropout mask of the forward pass)
-            dy = self.d_resid
+            dy = R[cur]
             if pd > 0.0:
-                N.dropout_apply(self.d_resid, self.d_drop, pd, seed, 3 + 3 * l)
+                N.dropout_apply(R[cur], self.d_drop, pd, seed, 3 + 3 * l)
                 dy = self.d_drop
                 self._n += 1
-            self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
-            N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
+
+            def wg_mlp_proj(dy=dy, l=l, p=p):
+                self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
+                N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
+
+            self._on_side(wg_mlp_proj)
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
                    aux_in=self.pre[l], epi=G.EPI_GELU_GRAD)
-            self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
-            N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
+
+            def wg_mlp_fc(l=l, p=p):
+                self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
+                N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
+
+            self._on_side(wg_mlp_fc)
             G.gemm(self.d_4c, w(p + "mlp.c_fc.weight"), self.d_c, b_mn=True)
+            self._join_side(keep_last=2)  # groups of the previous sub-layer read R[1 - cur]
             N.layernorm_bwd(self.d_c, self.x_mid[l], w(p + "ln_2.weight"), st[2], st[3],
-                            self.d_resid, self.d_resid, gw(p + "ln_2.weight"), glnb(p + "ln_2.bias"),
+                            R[cur], R[1 - cur], gw(p + "ln_2.weight"), glnb(p + "ln_2.bias"),
                             self.ln_scratch)
+            cur = 1 - cur
             # attention
-            dy = self.d_resid
+            dy = R[cur]
             if pd > 0.0:
-                N.dropout_apply(self.d_resid, self.d_drop, pd, seed, 2 + 3 * l)
+                N.dropout_apply(R[cur], self.d_drop, pd, seed, 2 + 3 * l)
                 dy = self.d_drop
                 self._n += 1
-            self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
-            N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
+
+            def wg_attn_proj(dy=dy, l=l, p=p):
+                self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
+                N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
+
+            self._on_side(wg_attn_proj)
             G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
             N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
                         self.attn_stats, B, T, H, pd, seed, 1 + 3 * l)
-            self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
-            N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
+
+            def wg_attn_qkv(l=l, p=p):
+                self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
+                N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
+
+            self._on_side(wg_attn_qkv)
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)
+            self._join_side(keep_last=2)
             N.layernorm_bwd(self.d_c, self.resid[l], w(p + "ln_1.weight"), st[0], st[1],
-                            self.d_resid, self.d_resid, gw(p + "ln_1.weight"), glnb(p + "ln_1.bias"),
+                            R[cur], R[1 - cur], gw(p + "ln_1.weight"), glnb(p + "ln_1.bias"),
                             self.ln_scratch)
+            cur = 1 - cur
             self._n += 4 + 4 + 2 * 2 + 3  # dgrad GEMMs, column sums, LN bwd (2 kernels each), flash bwd (3)
+        self._join_side()
         if pd > 0.0:
-            N.dropout_apply(self.d_resid, self.d_resid, pd, seed, 0)
+            N.dropout_apply(R[cur], R[cur], pd, seed, 0)
             self._n += 1
-        N.embed_bwd(self.idx, self.d_resid, gw("transformer.wte.weight"),
+        N.embed_bwd(self.idx, R[cur], gw("transformer.wte.weight"),
                     gw("transformer.wpe.weight"), B, T)
         self._n += 2
         self.launches_per_micro_step = self._n
