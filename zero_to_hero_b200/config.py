@@ -68,7 +68,7 @@ class TrainConfig:
     checkpoint_dir: str = ""
     checkpoint_interval: int = 0
     use_cuda_graph: bool = True
-    overlap_wgrad: bool = False  # weight-gradient GEMMs on a second stream (fills the tails of the data-gradient chain)
+    overlap_wgrad: bool = True  # weight-gradient GEMMs on a second stream (fills the tails of the data-gradient chain)
     log_jsonl: str = ""
 
 

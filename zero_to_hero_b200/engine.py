@@ -364,7 +364,7 @@ class GPT2TrainEngine:
         # ---------------- backward
         G.gemm(logits_v, w("transformer.wte.weight"), self.d_c, b_mn=True)
         self._n += 1
-        self._wgrad(logits_v, self.xf, "transformer.wte.weight")
+        self._wgrad(logits_v, self.xf, "transformer.wte.weight")  # fills the machine by itself: main stream
         self._overlap = bool(self.cfg.train.overlap_wgrad) and pd == 0.0
         self._side_done = []
         R = [self.d_resid, self.d_resid_alt if self._overlap else self.d_resid]
