@@ -245,14 +245,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     auto drain_dq = [&](int t) {
       tc_fence_after();
       const int tq = (j + t) * TS + r;
-      float* dq_row = p.dq_accum + (long long)(row0 + tq) * p.C + h * HD + half * 32;
+      // blocked layout [row / 32][head][16-byte column group][row % 32]: the 32 lanes of a warp
+      // (32 consecutive rows) hit 512 contiguous bytes per instruction instead of 32 rows
+      const long long g = (long long)row0 + tq;
+      float* dq_row = p.dq_accum + ((((g >> 5) * p.H + h) * 16 + half * 8) * 32 + (g & 31)) * 4;
       uint32_t v[32];
       tmem_ld_32x32b_x32(t_lane + DQ_COL + (t & 1) * HD + half * 32, v);
       tmem_ld_wait();
       if (tq < p.T) {
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 4),
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 128),
                        "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
                        "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
                        : "memory");
@@ -447,9 +450,15 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
       float2 x = unpack_bf16x2(aw[e]), y = unpack_bf16x2(cw[e]);
       s += x.x * y.x + x.y * y.y;
     }
-    float* dq = dq_accum + mh * HD + q * 8;
-    reinterpret_cast<float4*>(dq)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-    reinterpret_cast<float4*>(dq)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  // clear the fp32 dQ buffer (ceil(B*T / 32) * 32 rows in its blocked layout): 8 floats per thread
+  {
+    const long long rows32 = ((long long)B * T + 31) / 32 * 32;
+    if (idx < rows32 * H * 8) {
+      float* dq = dq_accum + idx * 8;
+      reinterpret_cast<float4*>(dq)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(dq)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -473,26 +482,36 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
   }
 }
 
-// dqkv[m, 0:C] = bf16(dq_accum[m, :] * scale)
+// dqkv[m, 0:C] = bf16(dQ[m, :] * scale), dQ read from its blocked layout
+// [row / 32][head][16-byte column group][row % 32]: a thread converts 16 columns of one row (four
+// coalesced 16-byte loads across the warp, one 32-byte store).
 __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
-                                            __nv_bfloat16* __restrict__ dqkv, long long M, int C,
+                                            __nv_bfloat16* __restrict__ dqkv, long long M, int H,
                                             float scale) {
   pdl_launch_dependents();
   pdl_wait();
-  const int vec_per_row = C / 8;
-  const long long total = M * vec_per_row;
+  const int C = H * HD;
+  const long long blocks = (M + 31) / 32;
+  const long long total = blocks * H * 4 * 32;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
-    const long long m = idx / vec_per_row;
-    const int c = (int)(idx % vec_per_row) * 8;
-    const float4 a = *reinterpret_cast<const float4*>(dq_accum + m * C + c);
-    const float4 b2 = *reinterpret_cast<const float4*>(dq_accum + m * C + c + 4);
-    uint4 u;
-    u.x = pack_bf16x2(a.x * scale, a.y * scale);
-    u.y = pack_bf16x2(a.z * scale, a.w * scale);
-    u.z = pack_bf16x2(b2.x * scale, b2.y * scale);
-    u.w = pack_bf16x2(b2.z * scale, b2.w * scale);
-    *reinterpret_cast<uint4*>(dqkv + m * 3 * C + c) = u;
+    const int lane = (int)(idx & 31);
+    const int c16 = (int)((idx >> 5) & 3);
+    const long long bh = idx >> 7;  // == blk * H + h
+    const int h = (int)(bh % H);
+    const long long g = (bh / H) * 32 + lane;
+    if (g >= M) continue;
+    const float4* src = reinterpret_cast<const float4*>(dq_accum) + (bh * 16 + c16 * 4) * 32 + lane;
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float4 a = src[k * 32];
+      w[2 * k] = pack_bf16x2(a.x * scale, a.y * scale);
+      w[2 * k + 1] = pack_bf16x2(a.z * scale, a.w * scale);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(dqkv + g * 3 * C + h * HD + c16 * 16);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
   }
 }
 
@@ -513,6 +532,8 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
     long long total = (long long)B * T * H * 8;
     const long long npad = 2LL * B * H * (Tpad - T);
     if (npad > total) total = npad;
+    const long long nzero = (((long long)B * T + 31) / 32 * 32) * H * 8;
+    if (nzero > total) total = nzero;
     const int grid = (int)((total + 255) / 256);
     launch_kernel(flash_bwd_prep_kernel, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)out,
                   (const __nv_bfloat16*)dout, lse, stats, dq_accum, B, T, H, Tpad);
@@ -538,10 +559,10 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
   launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H * n_t),
                 dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm_qkv, tm_do, p);
   {
-    const long long total = (long long)B * T * (C / 8);
+    const long long total = (((long long)B * T + 31) / 32) * H * 4 * 32;
     const int grid = (int)((total + 255) / 256);
     launch_kernel(flash_bwd_dq_convert_kernel, dim3(grid), dim3(256), 0, stream, true, (const float*)dq_accum,
-                  (__nv_bfloat16*)dqkv, (long long)B * T, C, 0.125f);
+                  (__nv_bfloat16*)dqkv, (long long)B * T, H, 0.125f);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
@@ -560,6 +581,9 @@ extern "C" int z2h_flash_bwd_dropout(const void* qkv, const void* out, const voi
                                      int* status, void* stream) {
   return z2h::flash_bwd_dropout(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site,
                                 status, (cudaStream_t)stream);
+}
+extern "C" long long z2h_flash_bwd_dq_elems(int B, int T, int H) {
+  return (((long long)B * T + 31) / 32 * 32) * H * 64;
 }
 extern "C" int z2h_flash_bwd_stats_elems(int B, int T, int H) {
   return 2 * B * H * ((T + 127) / 128 * 128);

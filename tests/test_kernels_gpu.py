@@ -141,7 +141,7 @@ def test_flash_attention_fwd_bwd(dev, B, T, H):
     ref.backward(dout.float().reshape(B, T, H, 64).transpose(1, 2))
     refd = torch.cat([g.grad.transpose(1, 2).reshape(B * T, C) for g in (q, k, v)], 1)
     dqkv = torch.zeros_like(qkv)
-    dqa = torch.empty(B * T, C, device=dev)
+    dqa = torch.empty(N.flash_bwd_dq_elems(B, T, H), device=dev)
     stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
     N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, stats, B, T, H)
     status_ok()
@@ -388,7 +388,7 @@ def test_flash_attention_dropout_against_masked_reference(dev, B, T, H):
     lse = torch.empty(B, H, T, device=dev)
     N.flash_fwd(qkv, out, lse, B, T, H, p, seed, site)
     dqkv = torch.empty_like(qkv)
-    dq_acc = torch.empty(B * T, C, device=dev)
+    dq_acc = torch.empty(N.flash_bwd_dq_elems(B, T, H), device=dev)
     stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
     N.flash_bwd(qkv, out, dout, lse, dqkv, dq_acc, stats, B, T, H, p, seed, site)
     # reference: explicit attention in fp32 with the same mask

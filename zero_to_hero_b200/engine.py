@@ -259,7 +259,7 @@ class GPT2TrainEngine:
             self.d_drop = buf(M, C)    # gradient of that output
         self.d_4c = buf(M, 4 * C)
         self.d_qkv = buf(M, 3 * C)
-        self.dq_accum = buf(M, C, dtype=f32)
+        self.dq_accum = buf(N.flash_bwd_dq_elems(B, T, H), dtype=f32)
         self.attn_stats = buf(N.flash_bwd_stats_elems(B, T, H), dtype=f32)
         self.ln_scratch = buf(N.layernorm_bwd_num_partials(M) * 2 * C, dtype=f32)
 

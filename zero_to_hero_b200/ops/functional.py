@@ -217,7 +217,7 @@ class _FlashAttention(torch.autograd.Function):
         d2 = dout.reshape(B * T, C)
         d2 = (d2 if d2.dtype == torch.bfloat16 else d2.bfloat16()).contiguous()
         dqkv = torch.empty_like(q2)
-        dq_accum = torch.empty(B * T, C, device=dout.device, dtype=torch.float32)
+        dq_accum = torch.empty(N.flash_bwd_dq_elems(B, T, H), device=dout.device, dtype=torch.float32)
         stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dout.device, dtype=torch.float32)
         N.flash_bwd(q2, out, d2, lse, dqkv, dq_accum, stats, B, T, H)
         return dqkv.reshape(B, T, 3 * C).to(dtype), None

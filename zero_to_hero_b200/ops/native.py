@@ -146,9 +146,16 @@ def flash_bwd_stats_elems(B: int, T: int, H: int) -> int:
     return 2 * B * H * ((T + 127) // 128 * 128)
 
 
+def flash_bwd_dq_elems(B: int, T: int, H: int) -> int:
+    """Number of fp32 scratch elements `flash_bwd` needs for its dQ accumulation (rows rounded up
+    to a multiple of 32: the kernels keep dQ there in a blocked layout)."""
+    return (B * T + 31) // 32 * 32 * H * 64
+
+
 def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p: float = 0.0, seed=None,
               site: int = 0):
     assert stats.numel() >= flash_bwd_stats_elems(B, T, H)
+    assert dq_accum.numel() >= flash_bwd_dq_elems(B, T, H) and dq_accum.dtype == torch.float32
     if drop_p > 0.0:
         assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
         _check(_f("z2h_flash_bwd_dropout")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),

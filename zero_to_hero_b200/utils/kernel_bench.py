@@ -103,7 +103,7 @@ def bench_flash(a, dev, which):
     else:
         dout = torch.randn_like(out)
         dqkv = torch.empty_like(qkv)
-        dqa = torch.empty(B * T, C, device=dev)
+        dqa = torch.empty(N.flash_bwd_dq_elems(B, T, H), device=dev)
         stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
         ms = time_kernel(lambda: N.flash_bwd(qkv, out, dout, lse, dqkv, dqa, stats, B, T, H), a.iters,
                          flush=not a.no_flush)
