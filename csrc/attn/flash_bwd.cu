@@ -10,12 +10,19 @@
 //   dV  += P^T  dO         (128 x 64 x 128)    TMEM cols 256..319, accumulated over q tiles
 //   dK  += dS^T Q          (128 x 64 x 128)    TMEM cols 320..383, accumulated over q tiles
 //   dQ_i = dS K            (128 x 64 x 128)    TMEM cols 384..447, added to an fp32 buffer
+//   P^T as packed bf16 pairs                   TMEM cols 448..511
 //
-// P^T and dS^T are written once to swizzled shared memory as bf16 and are consumed as the
-// K-major A operand of the dV / dK products and as the MN-major A operand of the dQ product;
-// Q, dO and K tiles serve as K-major or MN-major B operands straight from their TMA tiles, so
-// nothing is transposed in memory. dQ contributions of different KV tiles meet in an fp32
-// accumulation buffer (vector red.global.add), which a small kernel scales and converts.
+// P^T goes back to tensor memory (tcgen05.st) and is the A operand of the dV product from there;
+// dS^T is written once to swizzled shared memory as bf16 and is consumed as the K-major A operand
+// of the dK product and as the MN-major A operand of the dQ product; Q, dO and K tiles serve as
+// K-major or MN-major B operands straight from their TMA tiles, so nothing is transposed in
+// memory. dQ contributions of different KV tiles meet in an fp32 accumulation buffer (vector
+// red.global.add into a blocked layout in which a warp's 32 rows are contiguous), which a small
+// kernel scales, converts and writes row-major.
+//
+// Pipeline: the scores of query tile i+1 are issued as soon as the compute warps hold tile i's
+// scores in registers, three Q / dO stages keep two tiles of operands in flight, the dQ of tile
+// i-1 is read out while the products of tile i run.
 //
 // This is the hand-written counterpart of what autograd runs for
 // F.scaled_dot_product_attention in the reference (nn/gpt2/modules.py:37, train_ddp.py:141).
@@ -34,14 +41,16 @@ constexpr int TS = 128;  // tile size (queries and keys)
 constexpr int HD = 64;
 constexpr int TILE_BYTES = TS * HD * 2;  // 16 KiB
 constexpr int PT_BYTES = TS * TS * 2;    // 32 KiB
-constexpr int Q_STAGES = 2;
+constexpr int Q_STAGES = 3;
 constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps
 constexpr int NUM_COMPUTE = 256;
 constexpr int TMEM_COLS = 512;
-constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384;  // dQ: 2 x 64 columns
-constexpr int P_BUFS = 2;  // P^T / dS^T are double-buffered in shared memory
+// S^T and dP^T (fp32, 128 columns each), the dV / dK / dQ accumulators (64 each) and P^T as packed
+// bf16 pairs (64 columns): all 512 columns
+constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384, PT_COL = 448;
+constexpr int P_BUFS = 2;  // dS^T is double-buffered in shared memory; P^T lives in tensor memory
 constexpr int SMEM_BYTES =
-    2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + 2 * P_BUFS * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
+    2 * TILE_BYTES + 2 * Q_STAGES * TILE_BYTES + P_BUFS * PT_BYTES + Q_STAGES * 2 * TS * 4 + 256;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
 struct BwdParams {
@@ -75,8 +84,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   uint8_t* sV = sK + TILE_BYTES;
   uint8_t* sQ = sV + TILE_BYTES;
   uint8_t* sdO = sQ + Q_STAGES * TILE_BYTES;
-  uint8_t* sPt = sdO + Q_STAGES * TILE_BYTES;
-  uint8_t* sdSt = sPt + P_BUFS * PT_BYTES;
+  uint8_t* sdSt = sdO + Q_STAGES * TILE_BYTES;
   float* sLse = reinterpret_cast<float*>(sdSt + P_BUFS * PT_BYTES);  // [Q_STAGES][TS], already * log2(e)
   float* sDelta = sLse + Q_STAGES * TS;                      // [Q_STAGES][TS]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + Q_STAGES * TS);
@@ -85,8 +93,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   uint64_t* qdo_empty = qdo_full + Q_STAGES;
   uint64_t* st_full = qdo_empty + Q_STAGES;
   uint64_t* pds_full = st_full + 1;
-  uint64_t* dq_full = pds_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
+  uint64_t* dq_full = pds_full + 1;   // the three products of a tile are complete
+  uint64_t* s_read = dq_full + 1;     // the compute warps hold S^T / dP^T of the tile in registers
+  uint64_t* dv_done = s_read + 1;     // dV of the tile is complete: P^T may be overwritten
+  uint64_t* dq_empty = dv_done + 1;   // the compute warps have read the dQ accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,6 +118,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     mbar_init(st_full, 1);
     mbar_init(pds_full, NUM_COMPUTE / 32);
     mbar_init(dq_full, 1);
+    mbar_init(s_read, NUM_COMPUTE / 32);
+    mbar_init(dv_done, 1);
+    mbar_init(dq_empty, NUM_COMPUTE / 32);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -156,7 +170,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       // descriptors are built once; inside the loop an MMA costs one 64-bit add per operand
       const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
-      const uint64_t pt_desc = make_smem_desc_sw128(smem_u32(sPt), 16, 1024);
       const uint64_t dst_desc = make_smem_desc_sw128(smem_u32(sdSt), 16, 1024);
       const uint64_t dst_mn_desc = make_smem_desc_sw128(smem_u32(sdSt), TS * 128, 1024);
       uint64_t q_desc[Q_STAGES], do_desc[Q_STAGES];
@@ -166,8 +179,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         do_desc[s] = make_smem_desc_sw128(smem_u32(sdO + s * TILE_BYTES), 16, 1024);
       }
       auto issue_st = [&](int s) {
-        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
-        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
+        const uint64_t qd = s == 0 ? q_desc[0] : (s == 1 ? q_desc[1] : q_desc[2]);
+        const uint64_t dod = s == 0 ? do_desc[0] : (s == 1 ? do_desc[1] : do_desc[2]);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           tc_mma_f16_ss(tmem_base + ST_COL, desc_advance(k_desc, k * 32), desc_advance(qd, k * 32),
@@ -188,43 +201,48 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         issue_st(0);
       }
       Z2H_TRACE();
-      // Software pipeline: as soon as P^T / dS^T of tile `it` are in shared memory, S^T / dP^T of
-      // tile it+1 are issued first (their TMEM columns were just drained), then the three
-      // products that consume tile `it`; the compute warps meanwhile read dQ of tile it-1 and
-      // start on tile it+1 while those products are still running.
+      // Per tile `it`:
+      //   S^T, dP^T of it+1   as soon as the compute warps hold the scores of tile `it` in
+      //                       registers (s_read), i.e. while they still work on tile `it`; three
+      //                       Q / dO stages keep the operands of tiles it+1 and it+2 in flight
+      //   dV += P^T dO        once P^T (tensor memory) and dS^T (shared memory) are written;
+      //                       the A operand comes straight from tensor memory
+      //   dK += dS^T Q        last reader of the Q / dO stage, which is handed back here
+      //   dQ  = dS K          after the compute warps have read the previous tile's dQ
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % Q_STAGES;
         const uint32_t pb = (it & 1) * PT_BYTES;
-        if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
-        Z2H_TRACE();
         if (it + 1 < n_iter) {
           const int s2 = (it + 1) % Q_STAGES;
           const uint32_t ph2 = ((it + 1) / Q_STAGES) & 1;
+          if (!mbar_wait_bounded(s_read, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
           if (!mbar_wait_bounded(&qdo_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
           tc_fence_after();
           issue_st(s2);
         }
         Z2H_TRACE();
+        if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        Z2H_TRACE();
         tc_fence_after();
-        const uint64_t qd = s == 0 ? q_desc[0] : q_desc[1];
-        const uint64_t dod = s == 0 ? do_desc[0] : do_desc[1];
+        const uint64_t qd = s == 0 ? q_desc[0] : (s == 1 ? q_desc[1] : q_desc[2]);
+        const uint64_t dod = s == 0 ? do_desc[0] : (s == 1 ? do_desc[1] : do_desc[2]);
 #pragma unroll
-        for (int k = 0; k < TS / 16; ++k) {
-          const uint32_t a_off = pb + (k >> 2) * (TS * 128) + (k & 3) * 32;
-          tc_mma_f16_ss(tmem_base + DV_COL, desc_advance(pt_desc, a_off), desc_advance(dod, k * 2048),
+        for (int k = 0; k < TS / 16; ++k)  // queries 16k..16k+15 of P^T are 8 packed columns
+          tc_mma_f16_ts(tmem_base + DV_COL, tmem_base + PT_COL + k * 8, desc_advance(dod, k * 2048),
                         idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
-        }
+        tc_commit(dv_done);
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
           const uint32_t a_off = pb + (k >> 2) * (TS * 128) + (k & 3) * 32;
           tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
                         idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
         }
-        // dV and dK were the last readers of this Q / dO stage: hand it back before the dQ product
         tc_commit(&qdo_empty[s]);
+        if (it > 0 && !mbar_wait_bounded(dq_empty, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
-          tc_mma_f16_ss(tmem_base + DQ_COL + (it & 1) * HD, desc_advance(dst_mn_desc, pb + k * 2048),
+          tc_mma_f16_ss(tmem_base + DQ_COL, desc_advance(dst_mn_desc, pb + k * 2048),
                         desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
         }
         tc_commit(dq_full);
@@ -238,10 +256,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;  // key row (S^T, dV, dK) or query row (dQ) == TMEM lane
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
-    const uint32_t pt_row = smem_u32(sPt) + half * (TS * 128) + r * 128;
     const uint32_t dst_row = smem_u32(sdSt) + half * (TS * 128) + r * 128;
     // dQ of tile `t` (TMEM lane == query row; this warp takes 32 of the 64 columns) is added to
-    // the fp32 accumulation buffer; the MMA issuer alternates between two dQ accumulators
+    // the fp32 accumulation buffer; the accumulator is handed back as soon as it is in registers
     auto drain_dq = [&](int t) {
       tc_fence_after();
       const int tq = (j + t) * TS + r;
@@ -250,8 +267,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       const long long g = (long long)row0 + tq;
       float* dq_row = p.dq_accum + ((((g >> 5) * p.H + h) * 16 + half * 8) * 32 + (g & 31)) * 4;
       uint32_t v[32];
-      tmem_ld_32x32b_x32(t_lane + DQ_COL + (t & 1) * HD + half * 32, v);
+      tmem_ld_32x32b_x32(t_lane + DQ_COL + half * 32, v);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
       if (tq < p.T) {
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -305,12 +325,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64 + 32, sv[1]);
       tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64 + 32, dv[1]);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_read);  // S^T / dP^T columns may be overwritten from here on
       Z2H_CTRACE();  // scores in registers
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
+        uint32_t pt[16];  // P^T of these 32 queries, packed bf16 pairs
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint32_t pk[4], dk[4];
+          uint32_t dk[4];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int e4 = q * 2 + e;
@@ -346,21 +370,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             const float d1 = p1 * (g1 - D.y);
             const float d2 = p2 * (g2 - D.z);
             const float d3 = p3 * (g3 - D.w);
-            pk[e * 2 + 0] = pack_bf16x2(pd0, pd1);
-            pk[e * 2 + 1] = pack_bf16x2(pd2, pd3);
+            pt[q * 4 + e * 2 + 0] = pack_bf16x2(pd0, pd1);
+            pt[q * 4 + e * 2 + 1] = pack_bf16x2(pd2, pd3);
             dk[e * 2 + 0] = pack_bf16x2(d0, d1);
             dk[e * 2 + 1] = pack_bf16x2(d2, d3);
           }
           // 8 columns = one 16-byte chunk of this row inside swizzle atom `half`
           const uint32_t chunk = ((uint32_t)(ch * 4 + q) ^ (uint32_t)(r & 7)) * 16;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pt_row + pb + chunk), "r"(pk[0]),
-                       "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                       : "memory");
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + pb + chunk), "r"(dk[0]),
                        "r"(dk[1]), "r"(dk[2]), "r"(dk[3])
                        : "memory");
         }
+        // P^T goes to its tensor-memory columns (the dV product reads its A operand there); the
+        // previous tile's dV must have finished reading them
+        if (ch == 0 && it > 0 &&
+            !mbar_wait_bounded(dv_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tmem_st_32x32b_x16(t_lane + PT_COL + half * 32 + ch * 16, pt);
       }
+      if (!ok) break;
+      tmem_st_wait();
       Z2H_CTRACE();  // P^T / dS^T written
       // The products of tile it-1 must have completed before this warp signals tile `it`: a later
       // wait could otherwise see the barrier two phases ahead and mistake the parity.
