@@ -75,3 +75,15 @@ def test_heartbeat_detects_orderly_leave():
 
 def test_collective_times_out_cleanly_when_a_rank_never_joins():
     _assert_all_ok(run_ranks("collective_timeout", 2, env_extra={"PG_TIMEOUT": "3"}))
+
+
+def test_launcher_runs_cpu_ranks_and_reports_failure():
+    """The job launcher starts one trainer per rank (gloo on CPU here), returns 0 when all ranks
+    finish and a non-zero code when a rank fails."""
+    from zero_to_hero_b200.launch import launch
+
+    ok = launch(["--preset", "gpt2-tiny", "train.dtype=fp32", "train.steps=2", "train.total_batch_tokens=1024",
+                 "train.eval_interval=0"], ranks=2, cpu=True, timeout_s=300)
+    assert ok == 0
+    bad = launch(["--preset", "no-such-preset"], ranks=2, cpu=True, timeout_s=120)
+    assert bad != 0
