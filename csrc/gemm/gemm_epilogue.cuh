@@ -82,8 +82,11 @@ __device__ __forceinline__ float4 load_bf16x4(const __nv_bfloat16* ptr) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
-// Floats of shared memory one epilogue warp needs (the bias of its 128 columns).
-constexpr int kEpiBiasFloats = 128;
+// Shared memory of one epilogue warp: 4 KiB, used either for the bias of its 128 columns (first
+// 512 bytes) or as the 32 x 32 fp32 transposition buffer of the atomic-accumulate epilogue
+// (the two never occur in the same GEMM call path at the same time: staging happens per block).
+constexpr int kEpiWarpBytes = 32 * 32 * 4;
+constexpr int kEpiBiasFloats = kEpiWarpBytes / 4;  // stride between the warps' regions, in floats
 
 // ---- 16-byte and 32-byte global accesses -------------------------------------------------
 // A thread owns one accumulator row, i.e. 32 consecutive output columns: 64 contiguous bytes
@@ -263,8 +266,54 @@ __device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uin
   }
 }
 
+// Atomic accumulation (split-K / stream-K weight gradients) of a 32 x 32 block with coalesced
+// reductions. One accumulator row per lane would make every red.global.add touch 32 rows, i.e.
+// 32 memory transactions per instruction; the block is therefore transposed through a swizzled
+// 4 KiB shared-memory buffer so that 8 neighbouring lanes share a row and each instruction covers
+// 4 rows with one contiguous 128-byte segment each.
+//   row_base: global row of lane 0's accumulator row; stage: the warp's buffer (shared address).
+__device__ __forceinline__ void epilogue_block_atomic(const KernelParams& p, const uint32_t (&r)[32],
+                                                      long long row_base, int gcol, int lane,
+                                                      uint32_t stage) {
+  __syncwarp();  // the previous block's reads of the buffer are done
+#pragma unroll
+  for (int c4 = 0; c4 < 8; ++c4) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                     stage + lane * 128 + ((c4 ^ (lane & 7)) << 4)),
+                 "r"(r[c4 * 4 + 0]), "r"(r[c4 * 4 + 1]), "r"(r[c4 * 4 + 2]), "r"(r[c4 * 4 + 3])
+                 : "memory");
+  }
+  __syncwarp();
+  const int sub = lane >> 3, c4 = lane & 7;
+  float* cp = reinterpret_cast<float*>(p.C) + (row_base + sub) * p.ldc + gcol + c4 * 4;
+  const long long cstep = 4 * p.ldc;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int lr = i * 4 + sub;
+    uint32_t x0, x1, x2, x3;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                 : "r"(stage + lr * 128 + ((c4 ^ (lr & 7)) << 4))
+                 : "memory");
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + i * cstep),
+                 "f"(__uint_as_float(x0)), "f"(__uint_as_float(x1)), "f"(__uint_as_float(x2)),
+                 "f"(__uint_as_float(x3))
+                 : "memory");
+  }
+}
+
+//   stage: shared address of the warp's 4 KiB buffer (used by the atomic epilogue only)
 __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const uint32_t (&r)[4][32],
-                                              long long grow, int gcol0, const float* sbias) {
+                                              long long grow, int gcol0, const float* sbias, int lane,
+                                              uint32_t stage) {
+  if (p.out_fp32 && p.epi == kEpiAtomicAdd && sbias == nullptr) {
+    const long long row_base = grow - lane;
+    if (row_base + 32 <= p.M && gcol0 + 128 <= p.N) {  // interior: the same for the whole warp
+#pragma unroll
+      for (int c = 0; c < 4; ++c) epilogue_block_atomic(p, r[c], row_base, gcol0 + c * 32, lane, stage);
+      return;
+    }
+  }
   if (grow >= p.M) return;
   if (p.out_fp32) {
     if (p.epi == kEpiAtomicAdd) return epilogue_blocks<kEpiAtomicAdd, true>(p, r, grow, gcol0, sbias);

@@ -44,7 +44,7 @@ constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES =
-    1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * gemm_detail::kEpiBiasFloats * 4;
+    1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * gemm_detail::kEpiWarpBytes;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
 using gemm_detail::KernelParams;
@@ -65,7 +65,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* epi_bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);  // 128 floats per epilogue warp
+  float* epi_bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full_bar) + 256);  // 4 KiB per epilogue warp: bias slice or transposition buffer
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -235,7 +235,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (warp == 2 && lane == 0) Z2H_TRACE();
-      if (!empty_split) gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias);
+      if (!empty_split)
+        gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias, lane,
+                                   smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats));
       if (warp == 2 && lane == 0) Z2H_TRACE();
     }
   }
