@@ -312,7 +312,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   {
     const bool stream_k = g.split_k <= 0 && g.epi == kEpiAtomicAdd;  // fills every SM whatever the tile count
     const long long tiles256 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * (g.split_k < 1 ? 1 : g.split_k);
-    const bool pair = g_algo == 1 ? g.M >= 256 : (g_algo == 2 && g.M >= 256 && (stream_k || tiles256 >= 74));
+    // split-K and stream-K launches always take the pair kernel: it measured faster at every factor
+    const bool pair = g_algo == 1 ? g.M >= 256
+                                  : (g_algo == 2 && g.M >= 256 && (stream_k || g.split_k > 1 || tiles256 >= 74));
     if (pair) return gemm_bf16_pair(g, stream);
   }
   if (g.a_mn == 0 && g.b_mn == 0) return launch<0, 0>(g, stream);

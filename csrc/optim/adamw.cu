@@ -101,7 +101,24 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ dy, int M, int N, long long
   const int r0 = blockIdx.y * rows_per_slab;
   const int r1 = min(M, r0 + rows_per_slab);
   if (c < N) {
-    for (int r = r0 + rl; r < r1; r += 8) {
+    // four rows per trip: four independent 16-byte loads in flight per thread
+    int r = r0 + rl;
+    for (; r + 24 < r1; r += 32) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u[k] = *reinterpret_cast<const uint4*>(dy + (long long)(r + 8 * k) * ld + c);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&u[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+    for (; r < r1; r += 8) {
       uint4 u = *reinterpret_cast<const uint4*>(dy + (long long)r * ld + c);
       const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
 #pragma unroll
@@ -171,8 +188,8 @@ int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accum
                 cudaStream_t stream) {
   if (N % 8 != 0 || ld % 8 != 0) return 1;
   if (!accumulate) cudaMemsetAsync(db, 0, sizeof(float) * N, stream);
-  int slabs = (M + 255) / 256;
-  if (slabs > 64) slabs = 64;
+  int slabs = (M + 127) / 128;
+  if (slabs > 128) slabs = 128;
   if (slabs < 1) slabs = 1;
   const int rows_per_slab = (M + slabs - 1) / slabs;
   dim3 grid((N + 255) / 256, slabs);
