@@ -7,9 +7,10 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-REFERENCE = Path("/root/reference")
-if not REFERENCE.exists():
-    REFERENCE = ROOT / "baseline" / "_ref"
+# the unmodified reference tree, where a test compares against it (Z2H_REFERENCE overrides)
+import os
+
+REFERENCE = Path(os.environ.get("Z2H_REFERENCE", ROOT / "baseline" / "_ref"))
 
 
 def pytest_configure(config):
