@@ -19,6 +19,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
 #include "attn.h"
+#include "../common/trace.cuh"
 #include "../common/dropout.cuh"
 
 namespace z2h {
@@ -155,8 +156,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
         k_desc[s] = make_smem_desc_sw128(smem_u32(sK + s * TILE_BYTES), 16, 1024);
         v_desc[s] = make_smem_desc_sw128(smem_u32(sV + s * TILE_BYTES), 16, 1024);
       }
+      Z2H_TRACE_DECL(1)
+      Z2H_TRACE();
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
       if (ok) ok = mbar_wait_bounded(&k_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      Z2H_TRACE();
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -187,7 +191,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
           tc_commit(s_full);
           tc_commit(&k_empty[s2]);
         }
+        Z2H_TRACE();  // scores of the next tile issued
         if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        Z2H_TRACE();  // P of this tile is there
         if (!mbar_wait_bounded(&v_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
         tc_fence_after();
         const uint64_t vd = s == 0 ? v_desc[0] : v_desc[1];
@@ -199,6 +205,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
         }
         tc_commit(pv_full);
         tc_commit(&v_empty[s]);
+        Z2H_TRACE();  // P V issued
       }
     }
   } else {
@@ -218,12 +225,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
                  (unsigned long long)((p.T + 3) / 4);
     }
     bool ok = true;
+    Z2H_TRACE_DECL(2)
+#define Z2H_CTRACE()                         \
+  do {                                       \
+    if (warp == 2 && lane == 0) Z2H_TRACE(); \
+  } while (0)
+    Z2H_CTRACE();
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait_bounded(s_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      Z2H_CTRACE();  // scores are there
       const bool diag = (j == qi);
       // the whole score row (128 fp32) comes into registers with one wait
       uint32_t sv[KT / 32][32];
@@ -234,6 +248,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_read);
+      Z2H_CTRACE();  // scores in registers
       float m_new = m_run;
       if (!diag) {
         float m0 = m_new, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
@@ -280,6 +295,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
           }
         }
       }
+      Z2H_CTRACE();  // maximum known, previous P V complete
       const float mc = m_run * p.scale_log2;
       // p = 2^(s * c - m * c), row sum, bf16 P into swizzled shared memory
       float rs0 = 0.f, rs1 = 0.f;
@@ -324,6 +340,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);  // one arrival per softmax warp
+      Z2H_CTRACE();  // P written
     }
     if (ok && !mbar_wait_bounded(pv_full, (n_kv - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) ok = false;
     tc_fence_after();
@@ -414,3 +431,9 @@ extern "C" int z2h_flash_fwd(const void* qkv, void* out, float* lse, int B, int 
                              void* stream) {
   return z2h::flash_fwd(qkv, out, lse, B, T, H, status, (cudaStream_t)stream);
 }
+
+#ifdef Z2H_KERNEL_TRACE
+extern "C" int z2h_flash_fwd_trace_read(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_kernel_trace, sizeof(g_kernel_trace));
+}
+#endif
