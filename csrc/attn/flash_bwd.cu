@@ -580,11 +580,10 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
   p.drop_p = drop_p;
   p.seed_ptr = seed_ptr;
   p.site = site;
-  static bool attr = false;
-  if (!attr) {
+  static std::atomic<unsigned long long> attr_seen{0};
+  if (first_use_on_current_device(attr_seen)) {
     cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr = true;
   }
   const int n_t = (T + TS - 1) / TS;
   launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H * n_t),

@@ -402,11 +402,10 @@ int flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int 
   p.drop_p = drop_p;
   p.seed_ptr = seed_ptr;
   p.site = site;
-  static bool attr = false;
-  if (!attr) {
+  static std::atomic<unsigned long long> attr_seen{0};
+  if (first_use_on_current_device(attr_seen)) {
     cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr = true;
   }
   const int n_qt = (T + QT - 1) / QT;
   const cudaError_t err = launch_kernel(drop_p > 0.f ? flash_fwd_kernel<true> : flash_fwd_kernel<false>,

@@ -30,6 +30,7 @@
 // st.release.sys and polled by the owner with ld.acquire.sys; epochs only grow, so pads are
 // never cleared. Every poll loop has a time budget; on expiry the kernel records
 // kTimeoutPeer in the status word and returns, leaving the context usable.
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../optim/adamw_update.cuh"
 #include "comm.h"
@@ -438,7 +439,7 @@ int fused_step_twoshot(const FusedStepArgs& a, cudaStream_t stream) {
   const Peers grads = to_peers(a.grads, a.world);
   const Peers p16 = to_peers(a.p16, a.world);
   const Peers pads = to_peers(a.pads, a.world);
-  const int grid_a = grid_for(a.shard_n / 4, a.max_ctas > 0 ? a.max_ctas : 296);
+  const int grid_a = grid_for(a.shard_n / 4, a.max_ctas > 0 ? a.max_ctas : 2 * sm_count_current_device());
   const bool nvls = a.grads_mc != nullptr && a.p16_mc != nullptr;
   if (nvls)
     reduce_scatter_sumsq_kernel<true><<<grid_a, kThreads, 0, stream>>>(
@@ -448,7 +449,7 @@ int fused_step_twoshot(const FusedStepArgs& a, cudaStream_t stream) {
     reduce_scatter_sumsq_kernel<false><<<grid_a, kThreads, 0, stream>>>(
         grads, nullptr, pads, a.rank, a.world, a.shard_off, a.shard_n, a.partials, a.epoch, a.budget_ns,
         a.status);
-  const int grid_b = grid_for(a.total_n / 4, a.max_ctas > 0 ? a.max_ctas : 296);
+  const int grid_b = grid_for(a.total_n / 4, a.max_ctas > 0 ? a.max_ctas : 2 * sm_count_current_device());
   if (nvls)
     norm_adamw_allgather_kernel<true><<<grid_b, kThreads, 0, stream>>>(
         p16, reinterpret_cast<__nv_bfloat16*>(a.p16_mc), pads, reinterpret_cast<float*>(a.grads[a.rank]),
@@ -471,7 +472,7 @@ static int allreduce_impl(void* const* bufs, void* const* pads, void* out, int r
   if (world < 1 || world > kMaxRanks) return 1;
   const Peers b = to_peers(bufs, world), p = to_peers(pads, world);
   constexpr int E = Vec16<T>::kElems;
-  const int cap = max_ctas > 0 ? max_ctas : 296;
+  const int cap = max_ctas > 0 ? max_ctas : 2 * sm_count_current_device();
   if (algo == kAllReduceOneShot) {
     allreduce_oneshot_kernel<T><<<grid_for(n / E, cap), kThreads, 0, stream>>>(
         b, p, reinterpret_cast<T*>(out), rank, world, n, epoch, done_counter, budget_ns, status);

@@ -14,9 +14,37 @@
 // are no-ops in plain stream order.
 #pragma once
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdlib>
 
 namespace z2h {
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize (and the SM count) belong to a (kernel, device)
+// pair, not to the process: a host program that drives several GPUs from one process must set
+// them once per device. `seen` is a per-call-site bit mask of devices already configured; the
+// function returns true exactly once per device (devices 64 and up are configured every time).
+inline bool first_use_on_current_device(std::atomic<unsigned long long>& seen, int* device = nullptr) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (device != nullptr) *device = dev;
+  if (dev < 0 || dev >= 64) return true;
+  const unsigned long long bit = 1ull << dev;
+  return (seen.fetch_or(bit) & bit) == 0;
+}
+
+// Number of SMs of the current device (cached per device).
+inline int sm_count_current_device() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool cached = dev >= 0 && dev < 64;
+  int n = cached ? cache[dev].load(std::memory_order_relaxed) : 0;
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (cached) cache[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
 
 inline bool pdl_enabled() {
   static const bool on = [] {

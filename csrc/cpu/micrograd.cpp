@@ -7,6 +7,12 @@
 // reverse, adding into the children's gradients, which is exactly the behaviour of the
 // reference's Python engine (nn/micrograd/value.py:17-34: gradients accumulate with +=, the
 // root's gradient is set to 1). Handles are recycled when the owning Python object dies.
+//
+// Besides the unary / binary scalar ops there is one n-ary node, kAffine: b + sum_i w_i * x_i in
+// a single node (children w_0..w_{n-1}, x_0..x_{n-1}, b). A neuron of the MLP classes
+// (zero_to_hero_b200/micrograd/nn.py) is then two nodes (affine, tanh) instead of 2n+1, which
+// is what makes a training epoch cheap: the graph walk and the Python object count shrink by
+// the fan-in.
 #include <cmath>
 #include <cstdint>
 #include <mutex>
@@ -15,7 +21,7 @@
 namespace {
 
 enum Op : int32_t {
-  kLeaf = 0, kAdd, kMul, kPow, kTanh, kRelu, kSigmoid, kExp, kLog, kAbs, kDiv,
+  kLeaf = 0, kAdd, kMul, kPow, kTanh, kRelu, kSigmoid, kExp, kLog, kAbs, kDiv, kAffine,
 };
 
 struct Node {
@@ -27,6 +33,7 @@ struct Node {
 };
 
 std::vector<Node> g_nodes;
+std::vector<std::vector<int32_t>> g_kids;  // children of n-ary nodes, indexed like g_nodes
 std::vector<int32_t> g_free;
 uint32_t g_stamp = 0;
 std::mutex g_mutex;
@@ -37,9 +44,11 @@ int32_t alloc_node() {
     id = g_free.back();
     g_free.pop_back();
     g_nodes[id] = Node();
+    g_kids[id].clear();
   } else {
     id = (int32_t)g_nodes.size();
     g_nodes.emplace_back();
+    g_kids.emplace_back();
   }
   g_nodes[id].alive = true;
   return id;
@@ -75,6 +84,19 @@ void backprop_one(Node& n) {
     case kAbs: {
       const double x = g_nodes[n.a].data;
       g_nodes[n.a].grad += g * (x > 0.0 ? 1.0 : (x < 0.0 ? -1.0 : 0.0));
+      break;
+    }
+    case kAffine: {
+      const std::vector<int32_t>& k = g_kids[&n - g_nodes.data()];
+      const size_t fan_in = (k.size() - 1) / 2;
+      for (size_t i = 0; i < fan_in; ++i) {
+        Node& w = g_nodes[k[i]];
+        Node& x = g_nodes[k[fan_in + i]];
+        const double wd = w.data, xd = x.data;  // w and x may be the same node
+        w.grad += g * xd;
+        x.grad += g * wd;
+      }
+      g_nodes[k.back()].grad += g;
       break;
     }
     default: break;
@@ -122,6 +144,25 @@ int32_t mg_op(int32_t op, int32_t a, int32_t b, double aux) {
   return id;
 }
 
+// b + sum_i w[i] * x[i] as one node (products added in index order, starting from b).
+int32_t mg_affine(int32_t n, const int32_t* w, const int32_t* x, int32_t b) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (n < 0 || !valid(b)) return -1;
+  for (int32_t i = 0; i < n; ++i)
+    if (!valid(w[i]) || !valid(x[i])) return -1;
+  double out = g_nodes[b].data;
+  for (int32_t i = 0; i < n; ++i) out += g_nodes[w[i]].data * g_nodes[x[i]].data;
+  const int32_t id = alloc_node();
+  g_nodes[id].data = out;
+  g_nodes[id].op = kAffine;
+  std::vector<int32_t>& k = g_kids[id];
+  k.reserve(2 * (size_t)n + 1);
+  k.insert(k.end(), w, w + n);
+  k.insert(k.end(), x, x + n);
+  k.push_back(b);
+  return id;
+}
+
 double mg_get_data(int32_t id) { return valid(id) ? g_nodes[id].data : NAN; }
 double mg_get_grad(int32_t id) { return valid(id) ? g_nodes[id].grad : NAN; }
 void mg_set_data(int32_t id, double v) { if (valid(id)) g_nodes[id].data = v; }
@@ -151,12 +192,17 @@ int32_t mg_backward(int32_t root) {
       continue;
     }
     bool ready = true;
-    const int32_t kids[2] = {n.a, n.b};
-    for (int32_t c : kids)
+    const int32_t pair[2] = {n.a, n.b};
+    const bool nary = n.op == kAffine;
+    const int32_t* kids = nary ? g_kids[id].data() : pair;
+    const size_t n_kids = nary ? g_kids[id].size() : 2;
+    for (size_t k = 0; k < n_kids; ++k) {
+      const int32_t c = kids[k];
       if (c >= 0 && g_nodes[c].stamp != g_stamp) {
         ready = false;
         stack.push_back(c);
       }
+    }
     if (ready) {
       n.stamp = g_stamp;
       order.push_back(id);

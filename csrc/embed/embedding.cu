@@ -91,7 +91,7 @@ int embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, 
   if (C % 8 != 0) return 1;
   if (M <= 0) return 0;
   const long long total = (long long)M * (C / 8);
-  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int grid = (int)((total + 255) / 256 < sm_count_current_device() * 16 ? (total + 255) / 256 : sm_count_current_device() * 16);
   if (idx_is_64)
     launch_kernel(embed_fwd_kernel<long long>, dim3(grid), dim3(256), 0, stream, true, (const long long*)idx, (const __nv_bfloat16*)wte,
                                                          (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out,
@@ -109,7 +109,7 @@ int embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float
   const int M = B * T;
   if (M <= 0) return 0;
   const long long total = (long long)M * (C / 4);
-  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int grid = (int)((total + 255) / 256 < sm_count_current_device() * 16 ? (total + 255) / 256 : sm_count_current_device() * 16);
   if (idx_is_64)
     launch_kernel(embed_bwd_wte_kernel<long long>, dim3(grid), dim3(256), 0, stream, true, (const long long*)idx,
                                                              (const __nv_bfloat16*)dx, dwte, M, C, V);
@@ -118,7 +118,7 @@ int embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float
                                                        dwte, M, C, V);
   if (dwpe != nullptr) {
     const long long tc = (long long)T * C;
-    const int g2 = (int)((tc + 255) / 256 < 148 * 16 ? (tc + 255) / 256 : 148 * 16);
+    const int g2 = (int)((tc + 255) / 256 < sm_count_current_device() * 16 ? (tc + 255) / 256 : sm_count_current_device() * 16);
     launch_kernel(embed_bwd_wpe_kernel, dim3(g2), dim3(256), 0, stream, true, (const __nv_bfloat16*)dx, dwpe, B, T, C);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;

@@ -267,16 +267,11 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
 
   const KernelParams p = gemm_detail::make_kernel_params(g);
 
-  static bool attr_set = false;
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
-  static int num_sms = 0;
-  if (!attr_set) {
+  static std::atomic<unsigned long long> attr_seen{0};
+  if (first_use_on_current_device(attr_seen))
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    attr_set = true;
-  }
+  const int num_sms = sm_count_current_device();
   const long long tiles = (long long)((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) *
                           (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);
   int grid = tiles < num_sms ? (int)tiles : num_sms;
@@ -314,7 +309,7 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
     const long long tiles256 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * (g.split_k < 1 ? 1 : g.split_k);
     // split-K and stream-K launches always take the pair kernel: it measured faster at every factor
     const bool pair = g_algo == 1 ? g.M >= 256
-                                  : (g_algo == 2 && g.M >= 256 && (stream_k || g.split_k > 1 || tiles256 >= 74));
+                                  : (g_algo == 2 && g.M >= 256 && (stream_k || g.split_k > 1 || tiles256 >= sm_count_current_device() / 2));
     if (pair) return gemm_bf16_pair(g, stream);
   }
   if (g.a_mn == 0 && g.b_mn == 0) return launch<0, 0>(g, stream);

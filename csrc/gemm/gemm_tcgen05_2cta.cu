@@ -264,15 +264,10 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
   const KernelParams p = gemm_detail::make_kernel_params(g);
 
   auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  static int num_sms = 0;
-  if (!attr_set) {
+  static std::atomic<unsigned long long> attr_seen{0};
+  if (first_use_on_current_device(attr_seen))
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    attr_set = true;
-  }
+  const int num_sms = sm_count_current_device();
   const long long tiles = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) *
                           (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);
   int pairs = num_sms / 2;

@@ -284,13 +284,12 @@ int ce_fwd_bwd(void* logits, const void* targets, int idx_is_64, float* losses, 
   // rows that fit in shared memory twice per SM (the usual case: GPT-2's 50,304 columns are 98 KiB)
   const size_t row_bytes = (size_t)V_pad * 2;
   if (V_pad % 8 == 0 && row_bytes <= (size_t)kRowMaxBytes) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<unsigned long long> attr_seen{0};
+    if (first_use_on_current_device(attr_seen)) {
       cudaFuncSetAttribute(ce_row_in_smem_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kRowMaxBytes);
       cudaFuncSetAttribute(ce_row_in_smem_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kRowMaxBytes);
-      attr_set = true;
     }
     if (idx_is_64)
       launch_kernel(ce_row_in_smem_kernel<long long>, dim3(M), dim3(kRowThreads), row_bytes, stream, true, 

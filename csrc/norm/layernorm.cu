@@ -284,12 +284,10 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
 #define Z2H_LN_BWD(NV, DB)                                                                     \
   do {                                                                                         \
     auto kern = layernorm_bwd_kernel<NV, DB>;                                                  \
-    static bool attr = false;                                                                  \
-    if (!attr) {                                                                               \
+    static std::atomic<unsigned long long> attr_seen{0};                                       \
+    if (first_use_on_current_device(attr_seen))                                                \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
                            kWarpsPerCta * 2 * 32 * 8 * NV * (int)sizeof(float));               \
-      attr = true;                                                                             \
-    }                                                                                          \
     launch_kernel(kern, dim3(grid), dim3(kWarpsPerCta * 32), smem, stream, true,                                            \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, rstd, \
         (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, M, C);                      \

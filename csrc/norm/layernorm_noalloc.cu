@@ -46,7 +46,9 @@ int layernorm_bwd_noalloc(const void* dy, const void* x, const void* w, const fl
                           int M, int C, int accumulate, cudaStream_t stream) {
   if (M < 0 || C <= 0 || C % 8 != 0) return 1;
   const long long need = (long long)layernorm_bwd_num_partials(M) * 2 * C;
-  if (need > kLayerNormNoAllocScratchFloats) {
+  // C beyond 2048 is refused whatever M is (a small M could still fit the area, but the kernels
+  // underneath are not built for wider rows): the documented limit holds for every call
+  if (C > kLayerNormNoAllocMaxColumns || need > kLayerNormNoAllocScratchFloats) {
     fprintf(stderr,
             "z2h_layernorm_bwd_noalloc: M=%d C=%d needs %lld floats of scratch, the built-in area holds "
             "%lld (C up to 2048); use z2h_layernorm_bwd with a caller-provided buffer\n",

@@ -15,6 +15,8 @@ namespace z2h {
 // columns = 1,212,416 floats (about 4.6 MiB). Every GPU whose context loads the library
 // holds this much until the process exits, whether or not the function is ever called.
 constexpr long long kLayerNormNoAllocScratchFloats = 296LL * 2 * 2048;
+// Widest row accepted; wider problems get return code 4 whatever their row count.
+constexpr int kLayerNormNoAllocMaxColumns = 2048;
 
 // Same computation and arguments as layernorm_bwd() minus the scratch pointer.
 // Returns 0 on success, 1 for a bad argument, 3 if a launch failed, 4 if the problem needs more

@@ -112,3 +112,45 @@ def test_mlp_training_and_dot():
     assert isinstance(pred, Value) and 0 < pred.data < 1
     dot = to_dot(pred)
     assert dot.startswith("\ndigraph") and "tanh" in dot and "rankdir=LR" in dot
+
+
+def test_affine_node_matches_scalar_chain():
+    """One n-ary node gives the value and every gradient of the multiply-add chain it replaces,
+    also when a Value appears as weight and input at once."""
+    from zero_to_hero_b200.micrograd.value import affine
+
+    rng = np.random.default_rng(0)
+    wv, xv, bv = rng.uniform(-1, 1, 5), rng.uniform(-1, 1, 5), 0.3
+    w1, x1, b1 = [Value(v) for v in wv], [Value(v) for v in xv], Value(bv)
+    w2, x2, b2 = [Value(v) for v in wv], [Value(v) for v in xv], Value(bv)
+    fused = affine(w1, x1, b1).tanh()
+    chain = sum((w * x for w, x in zip(w2, x2)), b2).tanh()
+    assert fused._op == "tanh" and fused._children[0]._op == "affine"
+    assert len(fused._children[0]._children) == 11
+    assert fused.data == pytest.approx(chain.data, abs=1e-12)
+    fused.backward()
+    chain.backward()
+    for a, b in zip(w1 + x1 + [b1], w2 + x2 + [b2]):
+        assert a.grad == pytest.approx(b.grad, abs=1e-12)
+    s = Value(1.5)
+    sq = affine([s], [s], 0.0)  # s * s: the same node on both sides
+    sq.backward()
+    assert sq.data == 2.25 and s.grad == 3.0
+
+
+def test_neuron_layer_api_and_parameter_order():
+    from zero_to_hero_b200.micrograd import Layer, Neuron
+
+    np.random.seed(3)
+    expect = np.random.uniform(-1, 1, size=3)
+    np.random.seed(3)
+    n = Neuron(2)
+    assert [p.data for p in n.parameters()] == pytest.approx(list(expect))
+    assert len(n.w) == 2 and n.b.data == pytest.approx(expect[2])
+    out = n([1.0, -2.0])
+    assert out.data == pytest.approx(math.tanh(expect[0] - 2 * expect[1] + expect[2]))
+    layer = Layer(3, 2)
+    ys = layer([0.1, 0.2, 0.3])
+    assert isinstance(ys, list) and len(ys) == 2 and len(layer.parameters()) == 8
+    assert [p is q for p, q in zip(layer.neurons[1].parameters(), layer.parameters()[4:])] == [True] * 4
+    assert isinstance(Layer(3, 1)([0.1, 0.2, 0.3]), Value)

@@ -82,4 +82,6 @@ def test_noalloc_entry_point_rejects_oversized_problem():
     fn.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     # C = 4096 would need twice the built-in scratch: refused before any pointer is touched
     assert fn(None, None, None, None, None, None, None, None, None, 8192, 4096, 0, None) == 4
+    # a few wide rows would fit the area, but rows beyond 2048 columns are refused all the same
+    assert fn(None, None, None, None, None, None, None, None, None, 8, 4096, 0, None) == 4
     assert fn(None, None, None, None, None, None, None, None, None, 16, 100, 0, None) == 1

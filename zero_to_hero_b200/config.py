@@ -60,11 +60,12 @@ class TrainConfig:
     steps: int = 20
     seed: int = 42
     dtype: str = "bf16"         # compute dtype of the fused engine; "fp32" = PyTorch path
-    master_weights: bool = True  # fp32 master params + AdamW state, bf16 working copy
     eval_interval: int = 256
     eval_batches: int = 1
     log_interval: int = 1
     data: str = "synthetic"     # "synthetic" | "char:<path>" | "tokens:<path>"
+    val_frac: float = 0.05      # tokens:<path> only: tail of the file held out for validation
+    hellaswag: str = ""         # JSONL of pre-tokenised HellaSwag examples; scored at eval time
     checkpoint_dir: str = ""
     checkpoint_interval: int = 0
     use_cuda_graph: bool = True
@@ -77,8 +78,10 @@ class DistConfig:
     backend: str = "auto"       # "nccl" on GPU, "gloo" on CPU
     fused_allreduce: bool = True  # own P2P reduce-scatter + AdamW + all-gather kernel
     nvls: bool = False          # multimem flavour of the fused kernel
-    bucket_mb: int = 0          # 0 = one bucket
-    timeout_s: float = 600.0
+    bucket_mb: int = 32         # gradient buckets reduced while backward still runs; 0 = one reduce after it
+    timeout_s: float = 600.0    # process-group timeout and heartbeat patience (host side)
+    device_wait_s: float = 2.0  # budget of a kernel's wait for a peer's signal (device side)
+    heartbeat_interval: int = 1  # steps between host heartbeat checks; 0 = off
 
 
 @dataclass
@@ -116,8 +119,7 @@ PRESETS: dict[str, Any] = {
                           dropout=0.2, ln_bias=True, kind="char"),
         optim=OptimConfig(lr_max=3e-4, schedule="constant", warmup_steps=0, weight_decay=0.01,
                           clip_norm=0.0, beta2=0.999),
-        train=TrainConfig(micro_batch=64, total_batch_tokens=64 * 256, steps=20, dtype="fp32",
-                          master_weights=False)),
+        train=TrainConfig(micro_batch=64, total_batch_tokens=64 * 256, steps=20, dtype="fp32")),
     "gpt2-124m": lambda: Config(
         model=_gpt2(50304, 12, 12, 768),
         train=TrainConfig(micro_batch=16, total_batch_tokens=524_288)),
@@ -126,7 +128,7 @@ PRESETS: dict[str, Any] = {
         train=TrainConfig(micro_batch=8, total_batch_tokens=524_288)),
     "gpt2-1.5b": lambda: Config(
         model=_gpt2(50304, 48, 25, 1600),
-        train=TrainConfig(micro_batch=8, total_batch_tokens=1_048_576, master_weights=True)),
+        train=TrainConfig(micro_batch=8, total_batch_tokens=1_048_576)),
     # tiny model for tests and smoke runs
     "gpt2-tiny": lambda: Config(
         model=ModelConfig(vocab_size=512, block_size=128, emb_dim=128, num_heads=2, num_layers=2),

@@ -42,12 +42,21 @@ class CharTextLoader:
 
 class TokenFileLoader:
     def __init__(self, path: str | Path, batch_size: int, block_size: int, rank: int = 0,
-                 world_size: int = 1, dtype: str = "uint16", pin: bool = False):
+                 world_size: int = 1, dtype: str = "uint16", pin: bool = False,
+                 split: str = "all", val_frac: float = 0.0):
+        """`split="train"` reads the head of the file and `split="val"` its last `val_frac`
+        (the reference holds out its first 16,384 documents, nn/gpt2/data.py:23-24); "all" reads
+        everything."""
         path = Path(path)
         if path.suffix == ".pt":
-            self.tokens = torch.load(path).to(torch.int64)
+            tokens = torch.load(path).to(torch.int64)
         else:
-            self.tokens = torch.from_numpy(np.fromfile(path, dtype=np.dtype(dtype)).astype(np.int64))
+            tokens = torch.from_numpy(np.fromfile(path, dtype=np.dtype(dtype)).astype(np.int64))
+        if split != "all" and val_frac > 0.0:
+            n_val = max(batch_size * block_size + 1, int(len(tokens) * val_frac))
+            n_val = min(n_val, len(tokens) // 2)
+            tokens = tokens[-n_val:] if split == "val" else tokens[:-n_val]
+        self.tokens = tokens
         self.batch_size, self.block_size = batch_size, block_size
         self.rank, self.world_size = rank, world_size
         self.pin = pin

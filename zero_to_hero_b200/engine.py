@@ -35,6 +35,7 @@ from .ops.functional import pick_split_k
 from .optim.schedule import lr_for
 
 ALIGN = 64  # elements; keeps every tensor 256-byte (fp32) / 128-byte (bf16) aligned
+HYPER_SLOTS = 8  # pinned staging slots for the per-step optimizer scalars
 
 
 @dataclass
@@ -141,11 +142,19 @@ class GPT2TrainEngine:
             self.p16, self.g = comm.p16, comm.g
             self.p32, self.m, self.v = comm.p32_shard, comm.m_shard, comm.v_shard
         self.hyper = torch.zeros(16, device=dev, dtype=f32)
-        self.hyper_host = torch.zeros(16, dtype=f32).pin_memory()
+        # The host runs ahead of the stream, so step N's hyper-parameters must not sit in memory
+        # that step N+1 rewrites before the copy of step N has run: a ring of pinned slots, each
+        # reused only after the event recorded behind its copy has completed.
+        self._hyper_slots = [torch.zeros(16, dtype=f32).pin_memory() for _ in range(HYPER_SLOTS)]
+        self._hyper_events: list[torch.cuda.Event | None] = [None] * HYPER_SLOTS
+        self._hyper_next = 0
         self.partials = torch.zeros(1024, device=dev, dtype=f32)
         self.norm = torch.zeros(1, device=dev, dtype=f32)
         self.loss_accum = torch.zeros(1, device=dev, dtype=f32)
         self.loss_host = torch.zeros(1, dtype=f32).pin_memory()
+        self.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.eval_losses_buf = None
+        self._eval_graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
         self.opt_step = 0
         self.seed_value = cfg.train.seed if seed is None else seed
         self._alloc_activations(cfg.train.micro_batch, mc.block_size)
@@ -154,6 +163,7 @@ class GPT2TrainEngine:
         self._overlap = False
         self._graph = None
         self._graph_scale = None
+        self._n = 0
         self.launches_per_micro_step = 0
         self.init_weights(self.seed_value)
 
@@ -300,6 +310,66 @@ class GPT2TrainEngine:
         while len(self._side_done) > keep_last:
             main.wait_event(self._side_done.pop(0))
 
+    def _forward(self, B: int, T: int, pd: float) -> torch.Tensor:
+        """Forward pass over the first B*T rows of the static buffers; returns the logits view
+        [B*T, V]. `pd` is the dropout probability (0 for evaluation)."""
+        mc = self.mc
+        C, L, H, V = mc.emb_dim, mc.num_layers, mc.num_heads, mc.vocab_size
+        M = B * T
+        w = self.w
+        has_lnb = mc.ln_bias
+
+        def lnb(name):
+            return w(name) if has_lnb else None
+
+        def rows(t):
+            return t[:M]
+
+        seed = self.drop_seed
+        idx = self.idx.view(-1)[:M].view(B, T)
+        resid = [rows(t) for t in self.resid]
+        N.embed_fwd(idx, w("transformer.wte.weight"), w("transformer.wpe.weight"), resid[0], T)
+        self._n += 1
+        if pd > 0.0:
+            N.dropout_apply(resid[0], resid[0], pd, seed, 0)
+            self._n += 1
+        for l in range(L):
+            p = f"transformer.h.{l}."
+            st = [rows(t) for t in self.stats[l]]
+            xn1, xn2, x_mid = rows(self.xn1[l]), rows(self.xn2[l]), rows(self.x_mid[l])
+            qkv, att, pre, act = rows(self.qkv[l]), rows(self.att[l]), rows(self.pre[l]), rows(self.act[l])
+            lse = self.lse[l].view(-1)[:B * H * T]
+            N.layernorm_fwd(resid[l], w(p + "ln_1.weight"), lnb(p + "ln_1.bias"), xn1, st[0], st[1])
+            G.gemm(xn1, w(p + "attn.c_attn.weight"), qkv, bias=w(p + "attn.c_attn.bias"))
+            N.flash_fwd(qkv, att, lse, B, T, H, pd, seed, 1 + 3 * l)
+            if pd > 0.0:
+                tmp = rows(self.drop_tmp)
+                G.gemm(att, w(p + "attn.c_proj.weight"), tmp, bias=w(p + "attn.c_proj.bias"))
+                N.dropout_apply(tmp, x_mid, pd, seed, 2 + 3 * l, residual=resid[l])
+                self._n += 1
+            else:
+                G.gemm(att, w(p + "attn.c_proj.weight"), x_mid, bias=w(p + "attn.c_proj.bias"),
+                       residual=resid[l], epi=G.EPI_RESIDUAL)
+            N.layernorm_fwd(x_mid, w(p + "ln_2.weight"), lnb(p + "ln_2.bias"), xn2, st[2], st[3])
+            G.gemm(xn2, w(p + "mlp.c_fc.weight"), act, bias=w(p + "mlp.c_fc.bias"), aux_out=pre,
+                   epi=G.EPI_GELU)
+            if pd > 0.0:
+                tmp = rows(self.drop_tmp)
+                G.gemm(act, w(p + "mlp.c_proj.weight"), tmp, bias=w(p + "mlp.c_proj.bias"))
+                N.dropout_apply(tmp, resid[l + 1], pd, seed, 3 + 3 * l, residual=x_mid)
+                self._n += 1
+            else:
+                G.gemm(act, w(p + "mlp.c_proj.weight"), resid[l + 1], bias=w(p + "mlp.c_proj.bias"),
+                       residual=x_mid, epi=G.EPI_RESIDUAL)
+            self._n += 7
+        xf = rows(self.xf)
+        N.layernorm_fwd(resid[L], w("transformer.ln_f.weight"), lnb("transformer.ln_f.bias"), xf,
+                        rows(self.stats_f[0]), rows(self.stats_f[1]))
+        logits_v = self.logits[:M, :V]
+        G.gemm(xf, w("transformer.wte.weight"), logits_v)
+        self._n += 2
+        return logits_v
+
     def _forward_backward(self, grad_scale: float, loss_scale: float) -> None:
         """One micro-step on the static buffers `idx` / `tgt` (all launches, no host sync)."""
         mc = self.mc
@@ -309,57 +379,16 @@ class GPT2TrainEngine:
         has_lnb = mc.ln_bias
         self._n = 0
 
-        def lnb(name):
-            return w(name) if has_lnb else None
-
         def glnb(name):
             return gw(name) if has_lnb else None
 
         # ---------------- forward
         pd, seed = self.drop_p, self.drop_seed
-        N.embed_fwd(self.idx, w("transformer.wte.weight"), w("transformer.wpe.weight"),
-                    self.resid[0], T)
-        self._n += 1
-        if pd > 0.0:
-            N.dropout_apply(self.resid[0], self.resid[0], pd, seed, 0)
-            self._n += 1
-        for l in range(L):
-            p = f"transformer.h.{l}."
-            st = self.stats[l]
-            N.layernorm_fwd(self.resid[l], w(p + "ln_1.weight"), lnb(p + "ln_1.bias"), self.xn1[l],
-                            st[0], st[1])
-            G.gemm(self.xn1[l], w(p + "attn.c_attn.weight"), self.qkv[l], bias=w(p + "attn.c_attn.bias"))
-            N.flash_fwd(self.qkv[l], self.att[l], self.lse[l], B, T, H, pd, seed, 1 + 3 * l)
-            if pd > 0.0:
-                G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.drop_tmp,
-                       bias=w(p + "attn.c_proj.bias"))
-                N.dropout_apply(self.drop_tmp, self.x_mid[l], pd, seed, 2 + 3 * l, residual=self.resid[l])
-                self._n += 1
-            else:
-                G.gemm(self.att[l], w(p + "attn.c_proj.weight"), self.x_mid[l],
-                       bias=w(p + "attn.c_proj.bias"), residual=self.resid[l], epi=G.EPI_RESIDUAL)
-            N.layernorm_fwd(self.x_mid[l], w(p + "ln_2.weight"), lnb(p + "ln_2.bias"), self.xn2[l],
-                            st[2], st[3])
-            G.gemm(self.xn2[l], w(p + "mlp.c_fc.weight"), self.act[l], bias=w(p + "mlp.c_fc.bias"),
-                   aux_out=self.pre[l], epi=G.EPI_GELU)
-            if pd > 0.0:
-                G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.drop_tmp,
-                       bias=w(p + "mlp.c_proj.bias"))
-                N.dropout_apply(self.drop_tmp, self.resid[l + 1], pd, seed, 3 + 3 * l,
-                                residual=self.x_mid[l])
-                self._n += 1
-            else:
-                G.gemm(self.act[l], w(p + "mlp.c_proj.weight"), self.resid[l + 1],
-                       bias=w(p + "mlp.c_proj.bias"), residual=self.x_mid[l], epi=G.EPI_RESIDUAL)
-            self._n += 7
-        N.layernorm_fwd(self.resid[L], w("transformer.ln_f.weight"), lnb("transformer.ln_f.bias"),
-                        self.xf, self.stats_f[0], self.stats_f[1])
-        logits_v = self.logits[:, :V]
-        G.gemm(self.xf, w("transformer.wte.weight"), logits_v)
+        logits_v = self._forward(B, T, pd)
         # loss and d(logits) in one pass, in place
         N.ce_fwd_bwd(self.logits, self.tgt, self.losses, V, grad_scale)
         N.reduce_sum(self.losses, self.loss_accum, scale=loss_scale, accumulate=True)
-        self._n += 4
+        self._n += 2
 
         # ---------------- backward
         G.gemm(logits_v, w("transformer.wte.weight"), self.d_c, b_mn=True)
@@ -490,11 +519,19 @@ class GPT2TrainEngine:
     def _write_hyper(self, lr: float) -> None:
         oc = self.cfg.optim
         t = self.opt_step
-        h = self.hyper_host
+        k = self._hyper_next
+        self._hyper_next = (k + 1) % HYPER_SLOTS
+        ev = self._hyper_events[k]
+        if ev is not None:
+            ev.synchronize()  # the copy that last read this slot has run
+        h = self._hyper_slots[k]
         h[0], h[1], h[2], h[3], h[4] = lr, oc.beta1, oc.beta2, oc.eps, oc.weight_decay
         h[5], h[6] = 1.0 - oc.beta1 ** t, 1.0 - oc.beta2 ** t
         h[7], h[8] = oc.clip_norm, 1.0
         self.hyper.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._hyper_events[k] = ev
 
     def optimizer_step(self, lr: float | None = None) -> None:
         """Global grad-norm clip + AdamW + bf16 re-cast + gradient zeroing."""
@@ -519,10 +556,68 @@ class GPT2TrainEngine:
         self.optimizer_step(lr)
 
     def read_loss(self) -> float:
-        """Device -> host read of the mean loss of the last step (synchronises the stream)."""
+        """Device -> host read of the mean loss of the last step (synchronises the stream).
+        The status word of the device travels with it: if any bounded wait of a kernel gave up
+        (a peer that never signalled, a copy that never landed) the step is not trustworthy and
+        this raises before the caller launches the next one."""
+        status = _lib.status_word(self.device)
         self.loss_host.copy_(self.loss_accum, non_blocking=True)
+        self.status_host.copy_(status, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        code = int(self.status_host[0])
+        if code != 0:
+            status.zero_()
+            raise RuntimeError(f"z2h kernel reported status {code}: "
+                               f"{_lib.STATUS_NAMES.get(code, '?')}; the last step is invalid")
         return float(self.loss_host[0])
+
+    # ------------------------------------------------------------------ evaluation (forward only)
+    def eval_losses(self, idx: torch.Tensor, tgt: torch.Tensor) -> torch.Tensor:
+        """Per-token cross-entropy [B, T] (fp32, on the device) of a forward-only pass with dropout
+        off: what the reference gets from `model.eval()` + `model(X, Y)` (nn/gpt2/train.py:88-103).
+        Any B x T that fits the engine's buffers (B*T <= micro_batch*block_size, T <= block_size)
+        is accepted; each shape gets its own CUDA graph. Gradients, the loss accumulator, the
+        dropout seed and the micro-step counter are left alone, so training is not perturbed."""
+        B, T = idx.shape
+        if T > self.mc.block_size or B * T > self.M:
+            raise ValueError(f"batch {B}x{T} does not fit the engine's buffers ({self.M} tokens, "
+                             f"context {self.mc.block_size})")
+        M = B * T
+        if self.eval_losses_buf is None:
+            self.eval_losses_buf = torch.zeros(self.M, device=self.device, dtype=torch.float32)
+        self.idx.view(-1)[:M].copy_(idx.reshape(-1), non_blocking=True)
+        self.tgt.view(-1)[:M].copy_(tgt.reshape(-1), non_blocking=True)
+
+        def run():
+            saved = self._n
+            logits_v = self._forward(B, T, 0.0)
+            N.ce_fwd_bwd(self.logits[:M], self.tgt.view(-1)[:M], self.eval_losses_buf[:M],
+                         self.mc.vocab_size, 0.0, write_grad=False)
+            self._n = saved
+            return logits_v
+
+        if not self.cfg.train.use_cuda_graph:
+            run()
+        else:
+            graph = self._eval_graphs.get((B, T))
+            if graph is None:
+                s = torch.cuda.Stream(device=self.device)
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    run()
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                _lib.check_status(self.device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    run()
+                self._eval_graphs[(B, T)] = graph
+            graph.replay()
+        return self.eval_losses_buf[:M].view(B, T)
+
+    def eval_loss(self, idx: torch.Tensor, tgt: torch.Tensor) -> float:
+        """Mean cross-entropy of one batch, forward only (synchronises)."""
+        return float(self.eval_losses(idx, tgt).mean().item())
 
     def read_grad_norm(self) -> float:
         return float(self.norm.item())
@@ -540,21 +635,40 @@ class GPT2TrainEngine:
 
 
 def save_engine_checkpoint(engine: GPT2TrainEngine, path, data_state=None) -> None:
-    """Rank 0 writes model (GPT-2 names), flat AdamW moments, step, RNG, data cursor, config."""
+    """Rank 0 writes model (GPT-2 names), flat AdamW moments, step, RNG, dropout counters, data
+    cursors and config. `data_state` is this rank's loader state; the states of all ranks are
+    gathered and stored as a list, so that a resumed job gives every rank its own cursor back.
+    Every rank returns only after the file is complete (a barrier follows the write): a rank that
+    ran ahead into the next step would sit in the fused kernels' bounded device waits while
+    rank 0 is still writing."""
+    import torch.distributed as dist
+
     from .utils.checkpoint import save_checkpoint
 
+    multi = engine.world > 1 and dist.is_initialized()
     if engine.comm is None:
         m, v = engine.m.cpu(), engine.v.cpu()
     else:
         m, v = engine.comm.gather_shards(engine.m).cpu(), engine.comm.gather_shards(engine.v).cpu()
     sd = engine.state_dict()  # gathers the sharded master weights: every rank takes part
+    states = [data_state]
+    if multi:
+        states = [None] * engine.world
+        dist.all_gather_object(states, data_state)
     if engine.rank == 0:
-        save_checkpoint(path, sd, {"kind": "flat-adamw", "m": m, "v": v,
-                                                    "opt_step": engine.opt_step},
-                        engine.opt_step, data_state, engine.cfg.to_dict())
+        optim = {"kind": "flat-adamw", "m": m, "v": v, "opt_step": engine.opt_step,
+                 "drop_seed": int(engine.drop_seed.item()),
+                 "micro_steps_done": engine.micro_steps_done}
+        save_checkpoint(path, sd, optim, engine.opt_step,
+                        {"world": engine.world, "per_rank": states}, engine.cfg.to_dict())
+    if multi:
+        dist.barrier()
 
 
 def load_engine_checkpoint(engine: GPT2TrainEngine, path) -> dict:
+    """Restores parameters, moments, step, dropout counters and RNG; returns the checkpoint with
+    `ck["data"]` replaced by THIS rank's loader state (raises if the job's world size differs
+    from the one that wrote the data cursors)."""
     from .utils.checkpoint import load_checkpoint, set_rng_state
 
     ck = load_checkpoint(path)
@@ -568,5 +682,20 @@ def load_engine_checkpoint(engine: GPT2TrainEngine, path) -> dict:
             engine.comm.scatter_shards(opt["m"], engine.m)
             engine.comm.scatter_shards(opt["v"], engine.v)
         engine.opt_step = int(opt["opt_step"])
+        if "drop_seed" in opt:
+            # the seed advances by a rank-independent stride; keep this rank's own offset
+            advanced = int(opt["drop_seed"]) - (int(engine.seed_value) * 1_000_003 + 12345)
+            engine.drop_seed.fill_(engine.drop_seed0 + advanced)
+            engine.micro_steps_done = int(opt.get("micro_steps_done", 0))
     set_rng_state(ck["rng"])
+    ck["data"] = select_rank_state(ck.get("data"), engine.rank, engine.world)
     return ck
+
+
+def select_rank_state(data, rank: int, world: int):
+    """This rank's entry of the per-rank loader states a checkpoint holds."""
+    if not isinstance(data, dict) or "per_rank" not in data:
+        return data  # a single-state checkpoint of a one-rank job
+    if int(data["world"]) != world:
+        raise ValueError(f"checkpoint holds data cursors of {data['world']} ranks; this job has {world}")
+    return data["per_rank"][rank]

@@ -23,9 +23,15 @@ def sample(cfg: Config, state_dict=None, prompt=None, tokens: int = 64, temperat
     if state_dict is not None:
         model.load_state_dict(state_dict, strict=False)
     X = torch.zeros(1, 1, dtype=torch.long) if prompt is None else torch.tensor([prompt], dtype=torch.long)
-    gen = torch.Generator(device=device).manual_seed(seed)
     if cfg.model.kind == "char":
+        gen = torch.Generator(device=device).manual_seed(seed)
         return model.generate(X.to(device), tokens, generator=gen)
+    if torch.device(device).type == "cuda":
+        # no generator object: on a GPU `sample_next` then runs the fused temperature / top-k /
+        # multinomial kernel (csrc/sample/sample_topk.cu), seeded from torch's global generator
+        torch.manual_seed(seed)
+        return model.generate(X.to(device), tokens, temperature=temperature, top_k=top_k)
+    gen = torch.Generator(device=device).manual_seed(seed)
     return model.generate(X.to(device), tokens, temperature=temperature, top_k=top_k, generator=gen)
 
 

@@ -36,6 +36,9 @@ def _load():
     lib.mg_backward.restype = ctypes.c_int32
     lib.mg_backward.argtypes = [ctypes.c_int32]
     lib.mg_live_nodes.restype = ctypes.c_int32
+    lib.mg_affine.restype = ctypes.c_int32
+    lib.mg_affine.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32),
+                              ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]
     return lib
 
 
@@ -157,6 +160,14 @@ class Value:
                 a._pgrad += g / a._pdata
             elif op == "abs":
                 a._pgrad += g * (1.0 if a._pdata > 0 else (-1.0 if a._pdata < 0 else 0.0))
+            elif op == "affine":
+                kids = n._children
+                fan_in = (len(kids) - 1) // 2
+                for w, x in zip(kids[:fan_in], kids[fan_in:2 * fan_in]):
+                    wd, xd = w._pdata, x._pdata
+                    w._pgrad += g * xd
+                    x._pgrad += g * wd
+                kids[-1]._pgrad += g
 
     # ------------------------------------------------------------------ arithmetic
     @staticmethod
@@ -212,6 +223,29 @@ class Value:
 
     def abs(self):
         return self._make("abs")
+
+
+def affine(weights, inputs, bias) -> Value:
+    """bias + sum_i weights[i] * inputs[i] as ONE graph node (op tag "affine", children
+    weights..., inputs..., bias) instead of a chain of 2n scalar nodes. Numbers are wrapped into
+    leaf Values. The products are added in index order starting from the bias."""
+    ws = [Value._wrap(w) for w in weights]
+    xs = [Value._wrap(x) for x in inputs]
+    if len(ws) != len(xs):
+        raise ValueError(f"{len(ws)} weights for {len(xs)} inputs")
+    b = Value._wrap(bias)
+    children = (*ws, *xs, b)
+    if _LIB is not None:
+        n = len(ws)
+        arr = ctypes.c_int32 * n
+        nid = _LIB.mg_affine(n, arr(*[w._id for w in ws]), arr(*[x._id for x in xs]), b._id)
+        if nid < 0:
+            raise RuntimeError("micrograd engine rejected the operation")
+        return Value(0.0, "", children, "affine", _id=nid)
+    total = b._pdata
+    for w, x in zip(ws, xs):
+        total = total + w._pdata * x._pdata
+    return Value(total, "", children, "affine")
 
 
 def live_nodes() -> int:

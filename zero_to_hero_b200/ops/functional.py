@@ -27,7 +27,20 @@ def _native(t: torch.Tensor) -> bool:
     return t.is_cuda
 
 
-def pick_split_k(tiles: int, k_blocks: int, num_sms: int = 148, min_kb: int = 16) -> int:
+_sm_count: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """SMs of the current CUDA device (148 on a B200; the same figure is assumed without a GPU)."""
+    if not torch.cuda.is_available():
+        return 148
+    d = torch.cuda.current_device()
+    if d not in _sm_count:
+        _sm_count[d] = torch.cuda.get_device_properties(d).multi_processor_count
+    return _sm_count[d]
+
+
+def pick_split_k(tiles: int, k_blocks: int, num_sms: int | None = None, min_kb: int = 16) -> int:
     """Split-K factor for a weight-gradient GEMM (few output tiles, very long K).
 
     `tiles` counts 128 x 256 output tiles (one per SM); the kernel that runs them works on CTA
@@ -36,6 +49,8 @@ def pick_split_k(tiles: int, k_blocks: int, num_sms: int = 148, min_kb: int = 16
     2 * s for the extra atomic accumulation traffic. Returns 1 (plain deterministic accumulation)
     when the tiles alone fill the machine for several waves.
     """
+    if num_sms is None:
+        num_sms = sm_count()
     if tiles >= 4 * num_sms or k_blocks < 2 * min_kb:
         return 1
     pair_tiles, workers = max(1, (tiles + 1) // 2), max(1, num_sms // 2)

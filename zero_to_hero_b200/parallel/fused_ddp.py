@@ -114,7 +114,8 @@ class FusedDDP(PeerComm):
 
     launches_per_step = 3
 
-    def __init__(self, device: torch.device, group=None, budget_s: float = 2.0, nvls: bool = False):
+    def __init__(self, device: torch.device, group=None, budget_s: float = 2.0, nvls: bool = False,
+                 bucket_mb: int = 0):
         """`nvls=True` asks for the multimem flavour (in-switch reduction and broadcast); it is
         used when the symmetric allocations come with a multicast address, otherwise the plain
         peer load / store kernels run (`self.nvls` tells which)."""
@@ -129,6 +130,7 @@ class FusedDDP(PeerComm):
             c_void_p, c_ulonglong, c_void_p, c_int, c_void_p])
         self._want_nvls = nvls
         self.nvls = False
+        self.bucket_mb = int(bucket_mb)
         self._first = True
 
     def setup(self, total: int, n_decay: int) -> None:

@@ -11,7 +11,12 @@ One code path covers the reference's single-GPU trainer (nn/gpt2/train.py), its 
   * anything else (CPU, fp32, the char model) runs the PyTorch module path with
     torch AdamW (and torch DDP when launched with several ranks).
 Adds what the reference lacks: gradient accumulation to `train.total_batch_tokens`, periodic
-checkpoints, resume, JSONL logs. Tokens/sec is device-timed (CUDA events) per logging window.
+checkpoints, resume, JSONL logs, host-side failure detection between steps (heartbeats in the
+job's key-value store; a rank that stops or leaves ends the job with exit code 3 instead of a
+hang). Tokens/sec is device-timed (CUDA events) per logging window. Validation loss is a
+forward-only pass (dropout off) and, with `train.hellaswag=<file.jsonl>`, HellaSwag accuracy is
+scored through the same forward, strided over ranks and summed with two all-reduces, as the
+reference does (nn/gpt2/train_ddp.py:110-121,152-157).
 """
 from __future__ import annotations
 
@@ -21,6 +26,8 @@ import time
 
 import torch
 import torch.distributed as dist
+
+from datetime import timedelta
 
 from .config import Config, apply_overrides, get_preset
 from .data.synthetic import SyntheticLoader
@@ -40,7 +47,7 @@ def _dist_init(cfg: Config):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         backend = cfg.dist.backend if cfg.dist.backend != "auto" else ("nccl" if use_cuda else "gloo")
         kw = {"device_id": torch.device("cuda", local)} if backend == "nccl" else {}
-        dist.init_process_group(backend, **kw)
+        dist.init_process_group(backend, timeout=timedelta(seconds=cfg.dist.timeout_s), **kw)
     device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
     return rank, world, device
 
@@ -54,9 +61,14 @@ def make_loaders(cfg: Config, device, rank, world):
         return (lambda: ld.get_batch("train")), (lambda: ld.get_batch("val")), ld
     if tc.data.startswith("tokens:"):
         from .data.text import TokenFileLoader
-        ld = TokenFileLoader(tc.data[7:], tc.micro_batch, mc.block_size, rank, world,
-                             pin=device.type == "cuda")
-        return ld.next_host_batch, ld.next_host_batch, ld
+        pin = device.type == "cuda"
+        # the tail of the file is held out for validation and, like the reference's validation
+        # loader (nn/gpt2/train_ddp.py:77), is not sharded by rank
+        ld = TokenFileLoader(tc.data[7:], tc.micro_batch, mc.block_size, rank, world, pin=pin,
+                             split="train", val_frac=tc.val_frac)
+        va = TokenFileLoader(tc.data[7:], tc.micro_batch, mc.block_size, 0, 1, pin=pin,
+                             split="val", val_frac=tc.val_frac)
+        return ld.next_host_batch, va.next_host_batch, ld
     real_vocab = min(mc.vocab_size, 50257) if mc.vocab_size >= 50257 else mc.vocab_size
     tr = SyntheticLoader("train", tc.micro_batch, mc.block_size, real_vocab, device, rank, world, tc.seed)
     va = SyntheticLoader("val", tc.micro_batch, mc.block_size, real_vocab, device, 0, 1, tc.seed)
@@ -83,34 +95,60 @@ def train(cfg: Config, resume: str = "") -> dict:
 
     if fused:
         from .engine import GPT2TrainEngine, load_engine_checkpoint, save_engine_checkpoint
+        from .parallel.health import HeartbeatMonitor, default_store
         comm = None
+        monitor = None
         if world > 1:
             from .parallel.fused_ddp import FusedDDP, TorchDDPComm
-            comm = FusedDDP(device, nvls=cfg.dist.nvls) if cfg.dist.fused_allreduce else TorchDDPComm(device)
+            if cfg.dist.fused_allreduce:
+                comm = FusedDDP(device, budget_s=cfg.dist.device_wait_s, nvls=cfg.dist.nvls,
+                                bucket_mb=cfg.dist.bucket_mb)
+            else:
+                comm = TorchDDPComm(device)
+            if cfg.dist.heartbeat_interval > 0:
+                monitor = HeartbeatMonitor(default_store(), rank, world, timeout_s=cfg.dist.timeout_s)
         eng = GPT2TrainEngine(cfg, device, comm=comm)
         start = 0
         if resume:
             ck = load_engine_checkpoint(eng, resume)
             start = int(ck["step"])
             if ck.get("data") and hasattr(loader, "load_state"):
-                loader.load_state(ck["data"])
+                loader.load_state(ck["data"])  # this rank's own cursor / generator state
         if master:
             print(f"num_params: {eng.layout.num_params():,}")
+        examples = None
+        if tc.hellaswag:
+            from .eval.hellaswag import load_examples
+            examples = load_examples(tc.hellaswag)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         window = 0
         for step in range(start, tc.steps):
+            if monitor is not None and step % cfg.dist.heartbeat_interval == 0:
+                # every peer's host has reached this step, so the fused kernels launched below
+                # only ever wait for step skew; a peer that stopped raises RankFailure here,
+                # before any kernel that would wait for it is launched
+                monitor.beat(step)
+                monitor.wait_all(step)
             lr = lr_for(step, oc)
             eng.train_step([next_train() for _ in range(accum)], lr)
             window += 1
             if step % tc.log_interval == 0 or step == tc.steps - 1:
                 ev1.record()
-                loss = eng.read_loss()
+                loss = eng.read_loss()  # also raises if a device-side wait gave up
                 ms = ev0.elapsed_time(ev1) / max(window, 1)
                 rec = dict(train=loss, grad_norm=eng.read_grad_norm(), lr=lr, ms=ms,
                            tok_s=tokens_per_micro * accum / (ms / 1e3))
+                if world > 1:
+                    t = torch.tensor([loss, ms], device=device, dtype=torch.float64)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    rec["ms_max_over_ranks"] = float(t[1])
+                    rec["tok_s"] = tokens_per_micro * accum / (float(t[1]) / 1e3)
+                    rec["ms_rank"] = ms
                 if tc.eval_interval and step % tc.eval_interval == 0:
                     rec["val"] = evaluate_engine(eng, next_val, tc.eval_batches, world)
+                    if examples is not None:
+                        rec["hellaswag"] = hellaswag_engine(eng, examples, rank, world)
                 logger.log(step, **rec)
                 history.append({"step": step, **rec})
                 ev0.record()
@@ -127,20 +165,30 @@ def train(cfg: Config, resume: str = "") -> dict:
 
 
 def evaluate_engine(eng, next_val, batches: int, world: int) -> float:
-    """Validation loss through the engine's forward (loss only; gradients are discarded)."""
+    """Validation loss through the engine's forward-only path: dropout off, no backward, own CUDA
+    graph; gradients, dropout seed and micro-step counter of the training run are untouched."""
     total = 0.0
-    g_backup = eng.g.clone()
     for _ in range(batches):
-        eng.loss_accum.zero_()
-        eng.micro_step(*next_val(), 1)
-        total += eng.read_loss()
-    eng.g.copy_(g_backup)
+        total += eng.eval_loss(*next_val())
     loss = total / batches
     if world > 1:
         t = torch.tensor([loss], device=eng.device)
         dist.all_reduce(t, op=dist.ReduceOp.AVG)
         loss = float(t.item())
     return loss
+
+
+def hellaswag_engine(eng, examples, rank: int, world: int) -> float:
+    """HellaSwag accuracy through the engine's forward; examples strided over ranks, `correct`
+    and `total` summed with two all-reduces (nn/gpt2/train_ddp.py:152-157)."""
+    from .eval.hellaswag import evaluate_losses_fn
+
+    correct, total = evaluate_losses_fn(eng.eval_losses, examples, eng.device, eng.mc.block_size,
+                                        rank, world)
+    if world > 1:
+        dist.all_reduce(correct, op=dist.ReduceOp.SUM)
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+    return float(correct.item()) / max(1, int(total.item()))
 
 
 def build_module(cfg: Config):
@@ -200,6 +248,14 @@ def _train_modules(cfg, device, rank, world, accum, next_train, next_val, loader
                     for _ in range(tc.eval_batches):
                         X, Y = next_val()
                         vl += float(raw(X.to(device), Y.to(device))[1]) / tc.eval_batches
+                    if tc.hellaswag:
+                        from .eval.hellaswag import evaluate as hs_evaluate, load_examples
+                        c, n = hs_evaluate(raw, load_examples(tc.hellaswag), device, mc.block_size,
+                                           rank, world)
+                        if world > 1:
+                            dist.all_reduce(c, op=dist.ReduceOp.SUM)
+                            dist.all_reduce(n, op=dist.ReduceOp.SUM)
+                        rec["hellaswag"] = float(c.item()) / max(1, int(n.item()))
                 model.train()
                 rec["val"] = vl
             logger.log(step, **rec)
@@ -226,7 +282,14 @@ def main(argv=None):
     ap.add_argument("overrides", nargs="*", help="section.key=value")
     a = ap.parse_args(argv)
     cfg = apply_overrides(get_preset(a.preset), a.overrides)
-    train(cfg, a.resume)
+    from .parallel.health import RankFailure
+    try:
+        train(cfg, a.resume)
+    except RankFailure as e:
+        # a peer stopped between steps: nothing of ours is in flight towards it, so leave at once
+        # with a code the launcher turns into the job's exit code
+        print(f"[rank {os.environ.get('RANK', '0')}] stopping: {e}", flush=True)
+        os._exit(3)
     if dist.is_initialized():
         dist.destroy_process_group()
 
