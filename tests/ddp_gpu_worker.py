@@ -21,8 +21,9 @@ def main():
     from zero_to_hero_b200.config import get_preset
     from zero_to_hero_b200.engine import GPT2TrainEngine
     from zero_to_hero_b200.ops import _lib
-    from zero_to_hero_b200.parallel.fused_ddp import (BF16, F32, ONE_SHOT, TWO_SHOT, FusedDDP, PeerComm,
+    from zero_to_hero_b200.parallel.fused_ddp import (NVLS, ONE_SHOT, TWO_SHOT, FusedDDP, PeerComm,
                                                       SymmetricBuffer, TorchDDPComm)
+    use_nvls = os.environ.get("Z2H_TEST_NVLS", "0") == "1"  # multimem paths: only where asked for
 
     # ---- standalone all-reduce, one- and two-shot, fp32 and bf16, against NCCL
     comm = PeerComm(dev)
@@ -33,7 +34,10 @@ def main():
             x = (torch.randn(n, device=dev) * 0.1).to(dtype)
             ref = x.float().clone()
             dist.all_reduce(ref)
-            for algo in (ONE_SHOT, TWO_SHOT):
+            algos = [ONE_SHOT, TWO_SHOT]
+            if use_nvls and buf.multicast_ptr:
+                algos.append(NVLS)
+            for algo in algos:
                 buf.tensor.copy_(x)
                 torch.cuda.synchronize()
                 dist.barrier()
@@ -52,8 +56,16 @@ def main():
     cfg.model.vocab_size, cfg.model.block_size = 512, 128
     cfg.train.micro_batch = 2
     cfg.optim.warmup_steps, cfg.optim.schedule, cfg.optim.lr_max = 0, "constant", 1e-3
-    engines = [GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev), seed=7),
-               GPT2TrainEngine(cfg, dev, comm=TorchDDPComm(dev), seed=7)]
+    cfg.model.num_layers = 4
+    # 4 layer buckets of 786 KB reduced during backward (two-shot), the 327 KB embedding bucket and
+    # the small-parameter bucket at the end (one-shot); the second engine reduces one bucket after
+    # backward; the third is the NCCL + local AdamW baseline
+    engines = [GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, bucket_mb=0.5), seed=7),
+               GPT2TrainEngine(cfg, dev, comm=TorchDDPComm(dev), seed=7),
+               GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, bucket_mb=0, one_shot_kb=0), seed=7)]
+    kinds = [b.one_shot for b in engines[0].comm.buckets]
+    assert len(kinds) == 6 and kinds == [False] * 4 + [True, True], kinds
+    assert len(engines[2].comm.buckets) == 1
     g = torch.Generator().manual_seed(1000 + rank)  # every rank trains on different data
     for step in range(4):
         batches = []
@@ -65,9 +77,10 @@ def main():
             e.train_step(batches, lr=1e-3)
             res.append((e.read_loss(), e.read_grad_norm()))
         _lib.check_status(dev)
-        (l0, n0), (l1, n1) = res
-        assert abs(l0 - l1) < 1e-3, (step, l0, l1)
-        assert abs(n0 - n1) / n1 < 1e-3, (step, n0, n1)
+        (l0, n0), (l1, n1), (l2, n2) = res
+        assert abs(l0 - l1) < 1e-3 and abs(l2 - l1) < 1e-3, (step, l0, l1, l2)
+        assert abs(n0 - n1) / n1 < 1e-3 and abs(n2 - n1) / n1 < 1e-3, (step, n0, n1, n2)
+        c = engines[2].full_master()
         # AdamW divides by sqrt(v): where a gradient is almost zero, rounding-level differences
         # between the two reduction orders move a weight by up to lr per step, so the bound on
         # the largest difference is loose and the mean difference carries the check
@@ -75,6 +88,7 @@ def main():
         assert rel(a, b) < 5e-3, (step, rel(a, b))
         mean_rel = (a - b).abs().mean().item() / b.abs().mean().item()
         assert mean_rel < 1e-4, (step, mean_rel)
+        assert (c - b).abs().mean().item() / b.abs().mean().item() < 1e-4, step
         # every rank holds the same bf16 working copy after the all-gather
         w = engines[0].p16.float()
         ref = w.clone()
@@ -83,15 +97,18 @@ def main():
     if rank == 0:
         print("fused ddp OK", flush=True)
 
-    # ---- multimem (NVLS) flavour of the same step, where the system gives a multicast address
-    probe = FusedDDP(dev, nvls=True)
-    probe.setup(1 << 16, 1 << 16)
-    have_nvls = torch.tensor([int(probe.nvls)], device=dev)
-    dist.all_reduce(have_nvls, op=dist.ReduceOp.MIN)
-    del probe
+    # ---- multimem (NVLS) flavour of the same step, where asked for and the system gives a
+    # multicast address
+    have_nvls = torch.tensor([0], device=dev)
+    if use_nvls:
+        probe = FusedDDP(dev, nvls=True)
+        probe.setup(1 << 16, 1 << 16)
+        have_nvls = torch.tensor([int(probe.nvls)], device=dev)
+        dist.all_reduce(have_nvls, op=dist.ReduceOp.MIN)
+        del probe
     if have_nvls.item() == 1:
-        e_nvls = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, nvls=True), seed=7)
-        e_p2p = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev), seed=7)
+        e_nvls = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, nvls=True, bucket_mb=0.5), seed=7)
+        e_p2p = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, bucket_mb=0.5), seed=7)
         assert e_nvls.comm.nvls and not e_p2p.comm.nvls
         g2 = torch.Generator().manual_seed(2000 + rank)
         for step in range(3):
@@ -114,6 +131,49 @@ def main():
             print("fused ddp NVLS OK", flush=True)
     elif rank == 0:
         print("no multicast address: NVLS flavour not exercised", flush=True)
+    # ---- a rank that is late between steps (host-side delay; plain peer loads, NVLS off)
+    # (a) late by less than the device wait budget: the step is simply correct;
+    # (b) late by more: every rank's bounded waits give up, NO rank applies an update (sticky
+    #     status word), and the host learns of it with the loss read.
+    if os.environ.get("Z2H_TEST_SLOW_RANK", "1") == "1":
+        import time
+        e_slow = GPT2TrainEngine(cfg, dev, comm=FusedDDP(dev, budget_s=0.4, bucket_mb=0.5), seed=7)
+        g3 = torch.Generator().manual_seed(3000 + rank)
+
+        def make_batches():
+            out = []
+            for _ in range(2):
+                tok = torch.randint(0, 512, (2 * 128 + 1,), generator=g3)
+                out.append((tok[:-1].view(2, 128).pin_memory(), tok[1:].view(2, 128).pin_memory()))
+            return out
+
+        e_slow.train_step(make_batches(), lr=1e-3)
+        e_slow.read_loss()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == world - 1:
+            time.sleep(0.15)
+        e_slow.train_step(make_batches(), lr=1e-3)
+        loss_a = e_slow.read_loss()  # inside the budget: no error
+        assert loss_a == loss_a
+        before = e_slow.full_master()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == world - 1:
+            time.sleep(1.5)
+        e_slow.train_step(make_batches(), lr=1e-3)
+        raised = False
+        try:
+            e_slow.read_loss()
+        except RuntimeError as err:
+            raised = "status 5" in str(err)
+        assert raised, "a peer that is later than the wait budget must surface as status 5"
+        torch.cuda.synchronize()
+        dist.barrier()  # every rank has given up and cleared its status word by now
+        after = e_slow.full_master()
+        assert torch.equal(before, after), "an update was applied in a step whose waits gave up"
+        if rank == 0:
+            print("slow rank OK", flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

@@ -20,8 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_fused_ddp_matches_nccl_baseline(world):
+def _run(world, extra_env):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     port = _free_port()
@@ -29,6 +28,7 @@ def test_fused_ddp_matches_nccl_baseline(world):
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
                    MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        env.update(extra_env)
         procs.append(subprocess.Popen([sys.executable, WORKER], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outs = []
@@ -42,3 +42,16 @@ def test_fused_ddp_matches_nccl_baseline(world):
         outs.append(out)
     for r, o in enumerate(outs):
         assert f"OK rank {r}" in o, f"rank {r} output:\n{o[-3000:]}"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_ddp_matches_nccl_baseline(world):
+    """Standalone all-reduces vs NCCL; bucketed (overlapped) and single-bucket fused steps vs the
+    NCCL + local AdamW baseline; a late rank inside and beyond the device wait budget."""
+    _run(world, {})
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_fused_ddp_multimem_flavour(world):
+    """The same with the in-switch (multimem) reduction and broadcast; no rank is late here."""
+    _run(world, {"Z2H_TEST_NVLS": "1", "Z2H_TEST_SLOW_RANK": "0"})

@@ -152,3 +152,135 @@ def test_engine_with_dropout_tracks_module_with_the_same_masks():
     eng1.train_step(_batches(torch.Generator().manual_seed(0)), lr=1e-3)
     assert abs(eng0.read_loss() - eng1.read_loss()) > 1e-3
     _lib.check_status()
+
+
+def test_eval_path_is_forward_only_and_leaves_training_alone():
+    """Validation through the engine: dropout off, matches the fp32 module in eval mode, and the
+    gradients, dropout seed, micro-step counter and training graph are untouched by it."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+    from zero_to_hero_b200.models.gpt2 import GPT2
+
+    cfg = _cfg()
+    cfg.model.dropout = 0.2
+    cfg.model.num_layers = 2
+    eng = GPT2TrainEngine(cfg, "cuda", seed=5)
+    ref = GPT2(cfg.model).float().eval()
+    ref.load_state_dict({k: v.cpu() for k, v in eng.state_dict().items()})
+    g = torch.Generator().manual_seed(0)
+    (X, Y), = _batches(g, 1)
+    with torch.no_grad():
+        _, want = ref(X, Y)
+    # accumulate half a step, evaluate in the middle, finish the step
+    b = _batches(g, 2)
+    eng.loss_accum.zero_()
+    eng.micro_step(*b[0], 2)
+    g_before = eng.g.clone()
+    seed_before, n_before = int(eng.drop_seed.item()), eng.micro_steps_done
+    graphs_before = dict(eng._graphs)
+    got = eng.eval_loss(X, Y)
+    got2 = eng.eval_loss(X, Y)          # second call replays the captured forward-only graph
+    assert got == pytest.approx(want.item(), abs=5e-3) and got2 == pytest.approx(got, abs=1e-6)
+    assert torch.equal(eng.g, g_before)
+    assert int(eng.drop_seed.item()) == seed_before and eng.micro_steps_done == n_before
+    assert eng._graphs == graphs_before and len(eng._eval_graphs) == 1
+    # a smaller batch shape (the (4, 256) of the multiple-choice evaluation is the engine's own
+    # here, so take (2, 128)): per-token losses against the module
+    Xs, Ys = X[:2, :128].contiguous(), Y[:2, :128].contiguous()
+    with torch.no_grad():
+        logits, _ = ref(Xs, Ys)
+    want_tok = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), Ys.view(-1),
+                                                 reduction="none").view(2, 128)
+    got_tok = eng.eval_losses(Xs, Ys).cpu()
+    assert (got_tok - want_tok).abs().max().item() < 3e-2
+    eng.micro_step(*b[1], 2, last=True)
+    eng.optimizer_step(1e-3)
+    assert eng.read_loss() == eng.read_loss()
+
+
+def test_hellaswag_through_engine_matches_module():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+    from zero_to_hero_b200.eval.hellaswag import evaluate, evaluate_losses_fn
+    from zero_to_hero_b200.models.gpt2 import GPT2
+
+    cfg = _cfg()
+    cfg.model.num_layers = 2
+    eng = GPT2TrainEngine(cfg, "cuda", seed=11)
+    ref = GPT2(cfg.model).float().eval()
+    ref.load_state_dict({k: v.cpu() for k, v in eng.state_dict().items()})
+    g = torch.Generator().manual_seed(4)
+    examples = []
+    for i in range(6):
+        ctx = torch.randint(0, 1000, (int(torch.randint(5, 40, (1,), generator=g)),), generator=g).tolist()
+        ends = [torch.randint(0, 1000, (int(torch.randint(3, 20, (1,), generator=g)),), generator=g).tolist()
+                for _ in range(4)]
+        examples.append({"ctx_tokens": ctx, "ending_tokens": ends, "label": i % 4})
+    c_ref, n_ref = evaluate(ref, examples, "cpu", cfg.model.block_size)
+    c_eng, n_eng = evaluate_losses_fn(eng.eval_losses, examples, eng.device, cfg.model.block_size)
+    assert int(n_ref) == int(n_eng) == 6
+    # random weights score at chance; what must agree is WHICH ending each model prefers, up to
+    # bf16-level ties: allow one example of six to differ
+    assert abs(int(c_ref) - int(c_eng)) <= 1
+    # rank-strided sharding covers every example exactly once
+    parts = [evaluate_losses_fn(eng.eval_losses, examples, eng.device, cfg.model.block_size, r, 3)
+             for r in range(3)]
+    assert sum(int(n) for _, n in parts) == 6 and sum(int(c) for c, _ in parts) == int(c_eng)
+
+
+def test_hyper_parameters_survive_a_host_that_runs_ahead():
+    """Several optimizer steps queued without any host sync, each with its own learning rate:
+    every step must see its own value (staging ring), i.e. the result equals a run that
+    synchronises after every step."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+
+    cfg = _cfg()
+    cfg.model.num_layers = 2
+    lrs = [1e-3, 5e-5, 2e-3, 1e-5, 7e-4, 3e-3, 1e-4, 9e-4, 2e-4, 4e-3, 6e-5, 8e-4]
+    finals = []
+    for sync in (False, True):
+        eng = GPT2TrainEngine(cfg, "cuda", seed=2)
+        g = torch.Generator().manual_seed(0)
+        data = [_batches(g, 1) for _ in lrs]
+        dev = [[(x.cuda(), y.cuda()) for x, y in b] for b in data]
+        torch.cuda.synchronize()
+        for b, lr in zip(dev, lrs):
+            eng.train_step(b, lr=lr)
+            if sync:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        finals.append(eng.p32.clone())
+    # the step itself is reproducible only up to the order of its atomic accumulations, so the two
+    # runs are compared on average: a step that saw a neighbour's learning rate (they differ by up
+    # to 100x here) would move EVERY weight by about that difference, ~1e-3
+    assert (finals[0] - finals[1]).abs().mean().item() < 2e-5
+
+
+def test_checkpoint_restores_dropout_counters_and_rank_state(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import (GPT2TrainEngine, load_engine_checkpoint, save_engine_checkpoint,
+                                          select_rank_state)
+
+    cfg = _cfg()
+    cfg.model.dropout = 0.1
+    cfg.model.num_layers = 2
+    g = torch.Generator().manual_seed(0)
+    a = GPT2TrainEngine(cfg, "cuda", seed=3)
+    a.train_step(_batches(g), lr=1e-3)
+    save_engine_checkpoint(a, tmp_path / "d.pt", {"cursor": 123})
+    b = GPT2TrainEngine(cfg, "cuda", seed=3)
+    ck = load_engine_checkpoint(b, tmp_path / "d.pt")
+    assert ck["data"] == {"cursor": 123}
+    assert int(b.drop_seed.item()) == int(a.drop_seed.item()) and b.micro_steps_done == a.micro_steps_done == 2
+    nxt = _batches(g)
+    a.train_step(nxt, lr=1e-3)
+    b.train_step(nxt, lr=1e-3)
+    assert a.read_loss() == pytest.approx(b.read_loss(), abs=1e-4)   # same masks after the restore
+    with pytest.raises(ValueError):
+        select_rank_state({"world": 2, "per_rank": [1, 2]}, 0, 4)
+    assert select_rank_state({"world": 2, "per_rank": ["r0", "r1"]}, 1, 2) == "r1"

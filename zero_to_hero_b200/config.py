@@ -78,7 +78,7 @@ class DistConfig:
     backend: str = "auto"       # "nccl" on GPU, "gloo" on CPU
     fused_allreduce: bool = True  # own P2P reduce-scatter + AdamW + all-gather kernel
     nvls: bool = False          # multimem flavour of the fused kernel
-    bucket_mb: int = 32         # gradient buckets reduced while backward still runs; 0 = one reduce after it
+    bucket_mb: float = 32.0     # gradient buckets reduced while backward still runs; 0 = one reduce after it
     timeout_s: float = 600.0    # process-group timeout and heartbeat patience (host side)
     device_wait_s: float = 2.0  # budget of a kernel's wait for a peer's signal (device side)
     heartbeat_interval: int = 1  # steps between host heartbeat checks; 0 = off

@@ -94,6 +94,24 @@ class ParamLayout:
             off = _round_up(off + math.prod(shape))
         self.total = off
 
+    def backward_groups(self, num_layers: int) -> list[tuple[int, int, int]]:
+        """(offset, elements, ready_key) pieces of the flat gradient buffer in the order in which
+        the backward pass completes them: the matrices of layer L-1, ..., layer 0 (key = layer:
+        final once that layer's backward is done), then what is final only at the very end
+        (key -1): the embeddings (the tied wte receives the lm_head gradient first and the
+        embedding scatter last) and the block of LayerNorm weights and biases."""
+        groups = []
+        for l in reversed(range(num_layers)):
+            first = self.specs[f"transformer.h.{l}.attn.c_attn.weight"].offset
+            nxt = (self.specs[f"transformer.h.{l + 1}.attn.c_attn.weight"].offset
+                   if l + 1 < num_layers else self.n_decay)
+            groups.append((first, nxt - first, l))
+        emb_end = self.specs["transformer.h.0.attn.c_attn.weight"].offset if num_layers else self.n_decay
+        groups.append((0, emb_end, -1))
+        if self.total > self.n_decay:
+            groups.append((self.n_decay, self.total - self.n_decay, -1))
+        return groups
+
     def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
         s = self.specs[name]
         return flat[s.offset:s.offset + s.numel].view(s.shape)
@@ -138,7 +156,7 @@ class GPT2TrainEngine:
         else:
             # gradients and the bf16 working copy live in peer-visible memory; the fp32 master
             # copy and the moments exist only for the shard this rank owns
-            comm.setup(P, self.layout.n_decay)
+            comm.setup(P, self.layout.n_decay, self.layout.backward_groups(mc.num_layers))
             self.p16, self.g = comm.p16, comm.g
             self.p32, self.m, self.v = comm.p32_shard, comm.m_shard, comm.v_shard
         self.hyper = torch.zeros(16, device=dev, dtype=f32)
@@ -159,12 +177,14 @@ class GPT2TrainEngine:
         self.seed_value = cfg.train.seed if seed is None else seed
         self._alloc_activations(cfg.train.micro_batch, mc.block_size)
         self._side = torch.cuda.Stream(device=self.device)
+        self._comm_stream = torch.cuda.Stream(device=self.device)
         self._side_done = []
         self._overlap = False
-        self._graph = None
-        self._graph_scale = None
+        self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._reduced_in_backward = False
         self._n = 0
         self.launches_per_micro_step = 0
+        self.launches_last_micro_step = 0
         self.init_weights(self.seed_value)
 
     # ------------------------------------------------------------------ parameters
@@ -370,8 +390,37 @@ class GPT2TrainEngine:
         self._n += 2
         return logits_v
 
-    def _forward_backward(self, grad_scale: float, loss_scale: float) -> None:
-        """One micro-step on the static buffers `idx` / `tgt` (all launches, no host sync)."""
+    def _reduce_ready(self, key: int) -> None:
+        """Launch, on the communication stream, the reduction of the gradient buckets that the
+        backward pass has just completed (`key` = layer index, -1 = end of backward). The stream
+        first waits for everything issued so far on the compute streams."""
+        buckets = self.comm.buckets_for(key)
+        if not buckets:
+            return
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        ev_side = None
+        if self._overlap:
+            ev_side = torch.cuda.Event()
+            ev_side.record(self._side)
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ev)
+            if ev_side is not None:
+                self._comm_stream.wait_event(ev_side)
+            for b in buckets:
+                self.comm.reduce_bucket(b)
+            self._n += len(buckets)
+            if key < 0:
+                done = torch.cuda.Event()
+                done.record(self._comm_stream)
+        if key < 0:
+            main.wait_event(done)  # the optimizer phase follows on the main stream
+
+    def _forward_backward(self, grad_scale: float, loss_scale: float, reduce: bool = False) -> None:
+        """One micro-step on the static buffers `idx` / `tgt` (all launches, no host sync).
+        `reduce`: this is the last micro-step of an optimizer step of a multi-rank job, so every
+        gradient bucket is handed to the communicator as soon as it is final."""
         mc = self.mc
         C, L, H, V = mc.emb_dim, mc.num_layers, mc.num_heads, mc.vocab_size
         B, T, M = self.B, self.T, self.M
@@ -460,6 +509,8 @@ class GPT2TrainEngine:
                             self.ln_scratch)
             cur = 1 - cur
             self._n += 4 + 4 + 2 * 2 + 3  # dgrad GEMMs, column sums, LN bwd (2 kernels each), flash bwd (3)
+            if reduce:
+                self._reduce_ready(l)
         self._join_side()
         if pd > 0.0:
             N.dropout_apply(R[cur], R[cur], pd, seed, 0)
@@ -467,7 +518,11 @@ class GPT2TrainEngine:
         N.embed_bwd(self.idx, R[cur], gw("transformer.wte.weight"),
                     gw("transformer.wpe.weight"), B, T)
         self._n += 2
-        self.launches_per_micro_step = self._n
+        if reduce:
+            self._reduce_ready(-1)
+            self.launches_last_micro_step = self._n
+        else:
+            self.launches_per_micro_step = self._n
 
     def dropout_seed_of_micro_step(self, k: int) -> int:
         """Seed of the dropout masks of the k-th micro-step this engine ran (k = 1, 2, ...); give it
@@ -480,9 +535,11 @@ class GPT2TrainEngine:
         n = max(1, self.cfg.train.total_batch_tokens // tokens)
         return n
 
-    def micro_step(self, idx: torch.Tensor, tgt: torch.Tensor, accum_steps: int) -> None:
+    def micro_step(self, idx: torch.Tensor, tgt: torch.Tensor, accum_steps: int, last: bool = False) -> None:
         """Forward + backward on one micro-batch; `idx`/`tgt` may be pinned host or device
-        tensors of shape [micro_batch, block_size]. Gradients accumulate in the flat buffer."""
+        tensors of shape [micro_batch, block_size]. Gradients accumulate in the flat buffer.
+        `last=True` marks the final micro-step before `optimizer_step`: with a communicator that
+        supports it, the gradient buckets are then reduced across ranks while backward runs."""
         self.idx.copy_(idx, non_blocking=True)
         self.tgt.copy_(tgt, non_blocking=True)
         self.micro_steps_done += 1
@@ -490,18 +547,29 @@ class GPT2TrainEngine:
             self.drop_seed.add_(0x9E3779B1)  # new masks for this micro-step (also under graph replay)
         grad_scale = 1.0 / (self.M * accum_steps * self.world)
         loss_scale = 1.0 / (self.M * accum_steps)
+        reduce = bool(last and self.comm is not None and getattr(self.comm, "supports_overlap", False))
+        if reduce:
+            self.comm.align_first()
+            self._reduced_in_backward = True
+        torch.cuda.nvtx.range_push("z2h.micro_step")
         if not self.cfg.train.use_cuda_graph:
-            self._forward_backward(grad_scale, loss_scale)
+            self._forward_backward(grad_scale, loss_scale, reduce)
+            torch.cuda.nvtx.range_pop()
             return
-        if self._graph is None or self._graph_scale != (grad_scale, loss_scale):
+        key = (grad_scale, loss_scale, reduce)
+        graph = self._graphs.get(key)
+        if graph is None:
+            if any(k[:2] != key[:2] for k in self._graphs):
+                self._graphs.clear()  # the accumulation factor changed: the old graphs are stale
             # warm-up outside capture (sets function attributes, loads modules), then undo its
-            # side effects on the gradient / loss accumulators by capturing from a clean slate
+            # side effects on the gradient / loss accumulators by capturing from a clean slate.
+            # The warm-up never reduces: its signals would be taken for those of the real step.
             g_backup = self.g.clone()
             loss_backup = self.loss_accum.clone()
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                self._forward_backward(grad_scale, loss_scale)
+                self._forward_backward(grad_scale, loss_scale, False)
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             _lib.check_status(self.device)
@@ -509,12 +577,13 @@ class GPT2TrainEngine:
             self.loss_accum.copy_(loss_backup)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self._forward_backward(grad_scale, loss_scale)
+                self._forward_backward(grad_scale, loss_scale, reduce)
             self.g.copy_(g_backup)
             self.loss_accum.copy_(loss_backup)
             del g_backup
-            self._graph, self._graph_scale = graph, (grad_scale, loss_scale)
-        self._graph.replay()
+            self._graphs[key] = graph
+        graph.replay()
+        torch.cuda.nvtx.range_pop()
 
     def _write_hyper(self, lr: float) -> None:
         oc = self.cfg.optim
@@ -539,20 +608,23 @@ class GPT2TrainEngine:
         if lr is None:
             lr = lr_for(self.opt_step - 1, self.cfg.optim)
         self._write_hyper(lr)
+        torch.cuda.nvtx.range_push("z2h.optimizer_step")
         if self.comm is None:
             n = N.gradnorm_partials(self.g, self.partials)
             N.adamw_step(self.p32, self.g, self.m, self.v, self.p16, self.layout.n_decay, self.hyper,
                          self.partials, n, self.norm, zero_grad=True)
         else:
-            self.comm.fused_step(self.hyper, self.norm)
+            self.comm.fused_step(self.hyper, self.norm, reduced=self._reduced_in_backward)
+            self._reduced_in_backward = False
+        torch.cuda.nvtx.range_pop()
 
     def train_step(self, batches, lr: float | None = None) -> None:
         """One optimizer step over an iterable of (idx, tgt) micro-batches. Asynchronous: read
         the result with `read_loss()`."""
         batches = list(batches)
         self.loss_accum.zero_()
-        for idx, tgt in batches:
-            self.micro_step(idx, tgt, len(batches))
+        for i, (idx, tgt) in enumerate(batches):
+            self.micro_step(idx, tgt, len(batches), last=i == len(batches) - 1)
         self.optimizer_step(lr)
 
     def read_loss(self) -> float:
@@ -630,8 +702,11 @@ class GPT2TrainEngine:
 
     def kernel_launches_per_step(self, micro_steps: int) -> int:
         """How many of this library's kernels one optimizer step launches."""
-        opt = 2 if self.comm is None else self.comm.launches_per_step
-        return self.launches_per_micro_step * micro_steps + opt
+        if self.comm is None:
+            return self.launches_per_micro_step * micro_steps + 2
+        if self.launches_last_micro_step:  # the bucket reductions are counted in the last micro-step
+            return (self.launches_per_micro_step * (micro_steps - 1) + self.launches_last_micro_step + 2)
+        return self.launches_per_micro_step * micro_steps + self.comm.launches_per_step
 
 
 def save_engine_checkpoint(engine: GPT2TrainEngine, path, data_state=None) -> None:
