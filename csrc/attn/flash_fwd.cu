@@ -6,14 +6,24 @@
 // happen. The softmax scale is 1/sqrt(64), masking is causal, as in
 // F.scaled_dot_product_attention(q, k, v, is_causal=True) (nn/gpt2/modules.py:37).
 //
-// One CTA handles 128 query rows of one (batch, head) and walks the KV tiles 0..diagonal:
-//   warp 0     TMA: Q once, K/V tiles through a 2-stage ring (128-byte swizzle)
-//   warp 1     tcgen05.mma: S = Q K^T (128x128x64) into TMEM, then O += P V (128x64x128)
+// Work items are (batch, head, 128-row query tile); an item walks the KV tiles 0..diagonal. The
+// kernel is persistent: two CTAs per SM, each taking items from a static schedule that sorts the
+// items by length (longest first) and deals them out in a snake over the CTAs, so every CTA gets
+// the same amount of work to within one tile, pays the set-up (barriers, tensor memory) once,
+// and loads the next item's Q and K while the current item drains. Roles inside a CTA:
+//   warp 0     TMA: Q per item, K/V tiles through a 3-stage ring (128-byte swizzle)
+//   warp 1     tcgen05.mma: S = Q K^T (128x128x64) into TMEM, then O += P V (128x64x128); the
+//              scores of tile t+1 (also across an item boundary) are issued as soon as the
+//              softmax warps hold tile t in registers
 //   warps 2-5  one query row per thread: read S from TMEM, online softmax in fp32 (no
-//              shuffles: a thread owns its row), write P as bf16 into swizzled shared memory
-//              for the second MMA. O accumulates in TMEM across KV tiles and is rescaled
-//              there only when a row maximum grows by more than 2^8.
-// TMEM use is 192 columns (allocated as 256) and shared memory ~113 KiB, so two CTAs share an
+//              shuffles: a thread owns its row), write P as packed bf16 back into TMEM, where
+//              the second MMA reads its A operand (P never touches shared memory, whose
+//              bandwidth the operand reads of the MMAs and the TMA writes already use up).
+//              O accumulates in TMEM across KV tiles and is rescaled
+//              there only when a row maximum grows by more than 2^8. On the diagonal tile a
+//              warp (32 consecutive rows) skips the 32-column chunks that are masked for all of
+//              its rows: no TMEM load, no exponentials, zeros into P.
+// TMEM use is 256 columns and shared memory ~113 KiB, so two CTAs share an
 // SM and one CTA's tensor-core work overlaps the other's exponentials.
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
@@ -25,17 +35,23 @@
 namespace z2h {
 namespace {
 
-constexpr int QT = 128;   // query rows per CTA
+constexpr int QT = 128;   // query rows per item
 constexpr int KT = 128;   // kv rows per tile
 constexpr int HD = 64;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 16 KiB
-constexpr int P_BYTES = QT * KT * 2;      // 32 KiB
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 3;
+// Of every 8 pairs of exponentials, this many are computed with a polynomial on the FMA pipe
+// instead of the special-function unit (which two CTAs per SM keep saturated otherwise).
+#ifndef Z2H_FWD_POLY_OF_8
+#define Z2H_FWD_POLY_OF_8 0
+#endif
+constexpr int kPolyOf8 = Z2H_FWD_POLY_OF_8;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 256;
-constexpr int S_COL = 0, PV_COL = 128;
+// scores (fp32, 128 columns), output accumulator (fp32, 64), probabilities as packed bf16 pairs (64)
+constexpr int S_COL = 0, PV_COL = 128, P_COL = 192;
 // two CTAs per SM need (dynamic + 1 KiB reserved) * 2 <= 228 KiB, i.e. at most 115,712 bytes each
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 256;
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 256;
 static_assert(SMEM_BYTES <= 115712, "two CTAs per SM no longer fit");
 
 struct FwdParams {
@@ -50,6 +66,122 @@ struct FwdParams {
   const unsigned long long* seed_ptr;
   uint32_t site;
 };
+
+// The flat sequence of (item, kv tile) pairs one CTA works through. Items are numbered longest
+// first (index i -> query tile n_qt-1 - i / BH, batch*head i % BH); CTA c of G takes, in round k,
+// item k*G + c (k even) or k*G + G-1-c (k odd). Every role of the CTA runs its own copy of the
+// iterator (the MMA warp two: current tile and look-ahead), so no schedule is communicated.
+struct TileIter {
+  int k, j, qi, bh;  // round of the schedule, kv tile within the item, the item itself
+  bool valid;
+  // grid size, CTA index and the problem's shape are re-read where needed rather than kept here:
+  // the softmax warps, which hold a whole score row in registers, run one of these too
+  __device__ __forceinline__ void init(int T, int BH) {
+    k = 0;
+    valid = next_item(T, BH);
+  }
+  __device__ __forceinline__ bool next_item(int T, int BH) {
+    const int G = gridDim.x, c = blockIdx.x, n_qt = (T + QT - 1) / QT;
+    const int i = k * G + ((k & 1) ? G - 1 - c : c);
+    if (i >= n_qt * BH) return false;
+    ++k;
+    qi = n_qt - 1 - i / BH;
+    bh = i - (i / BH) * BH;
+    j = 0;
+    return true;
+  }
+  __device__ __forceinline__ void next_tile(int T, int BH) {
+    if (++j > qi) valid = next_item(T, BH);
+  }
+  __device__ __forceinline__ bool first() const { return j == 0; }
+  __device__ __forceinline__ bool last() const { return j == qi; }
+};
+
+
+// Row maximum of one score tile (one thread = one query row, 128 scores in registers).
+// DIAG: the tile on the diagonal; a warp's rows (quarter*32 .. +31) see the 32-column chunks
+// 0..quarter only, the last of them triangular (column i visible iff i <= lane). The common
+// (off-diagonal) instantiation carries no masking instructions at all.
+template <bool DIAG>
+__device__ __forceinline__ float tile_row_max(const uint32_t (&sv)[KT / 32][32], float m_in, int quarter,
+                                              int lane) {
+  // eight independent chains (two per chunk), so the maxima do not wait on one another
+  float mx[KT / 16] = {m_in, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int ch = 0; ch < KT / 32; ++ch) {
+    if (DIAG && ch > quarter) continue;
+    if (DIAG && ch == quarter) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i <= lane) mx[2 * ch + (i & 1)] = fmaxf(mx[2 * ch + (i & 1)], __uint_as_float(sv[ch][i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        mx[2 * ch] = max3(mx[2 * ch], __uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1]));
+        mx[2 * ch + 1] = max3(mx[2 * ch + 1], __uint_as_float(sv[ch][16 + i]), __uint_as_float(sv[ch][17 + i]));
+      }
+    }
+  }
+  mx[0] = max3(mx[0], mx[1], mx[2]);
+  mx[3] = max3(mx[3], mx[4], mx[5]);
+  mx[6] = fmaxf(mx[6], mx[7]);
+  return max3(mx[0], mx[3], mx[6]);
+}
+
+// p = 2^(s * c - m * c) for the whole row, packed bf16 pairs into pk, returns the row sum.
+// Dropout (DROP) masks what enters P V, not the sum.
+template <bool DIAG, bool DROP>
+__device__ __forceinline__ float tile_exponentials(const uint32_t (&sv)[KT / 32][32], uint32_t (&pk)[KT / 32][16],
+                                                   float scale_log2, float mc, int quarter, int lane,
+                                                   const DropoutSpec& drop, unsigned long long drop_word0) {
+  float2 rs = make_float2(0.f, 0.f), rs_b = make_float2(0.f, 0.f);
+  const float2 sc2 = make_float2(scale_log2, scale_log2), nmc2 = make_float2(-mc, -mc);
+#pragma unroll
+  for (int ch = 0; ch < KT / 32; ++ch) {
+    if (DIAG && ch > quarter) {  // masked for every row of this warp: zeros, no exponentials
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[ch][i] = 0u;
+      continue;
+    }
+    const bool tri = DIAG && ch == quarter;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t mw[2] = {0, 0};
+      if (DROP) {
+        const unsigned long long w0 = drop_word0 + (unsigned long long)(ch * 8 + q * 2);
+        mw[0] = dropout_word(drop.seed_lo, drop.seed_hi, w0);
+        mw[1] = dropout_word(drop.seed_lo, drop.seed_hi, w0 + 1);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = q * 8 + e * 2;
+        // one packed multiply-add for the pair, two exponentials, one packed add for the sums
+        const float2 x = fma2(make_float2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), sc2, nmc2);
+        float p0, p1;
+        if (((q * 4 + e) & 7) < kPolyOf8) {
+          const float2 pp = ex2_poly2(x);
+          p0 = pp.x;
+          p1 = pp.y;
+        } else {
+          p0 = ex2_fast(x.x);
+          p1 = ex2_fast(x.y);
+        }
+        if (tri) {
+          if (i > lane) p0 = 0.f;
+          if (i + 1 > lane) p1 = 0.f;
+        }
+        if (e & 1) rs_b = add2(rs_b, make_float2(p0, p1));
+        else rs = add2(rs, make_float2(p0, p1));
+        if (DROP) {
+          if (!dropout_keep(mw[e >> 1], (e & 1) * 2, drop.threshold)) p0 = 0.f;
+          if (!dropout_keep(mw[e >> 1], (e & 1) * 2 + 1, drop.threshold)) p1 = 0.f;
+        }
+        pk[ch][q * 4 + e] = pack_bf16x2(p0, p1);
+      }
+    }
+  }
+  return (rs.x + rs.y) + (rs_b.x + rs_b.y);
+}
 
 // DROP: the probabilities that enter P V are masked (mask of element (b, h, q, k): word
 // ((b*H + h)*T + q) * ceil(T/4) + k/4 of the site's stream); the softmax normaliser is not, and the
@@ -66,10 +198,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
   uint8_t* sQ = smem_raw;
   uint8_t* sK = sQ + TILE_BYTES;
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
-  uint8_t* sP = sV + KV_STAGES * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KV_STAGES * TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
+  uint64_t* q_empty = bars + 1;             // every score MMA of the item has read Q
+  uint64_t* k_full = bars + 2;
   uint64_t* v_full = k_full + KV_STAGES;
   uint64_t* k_empty = v_full + KV_STAGES;   // K stage free: the score MMAs that read it are done
   uint64_t* v_empty = k_empty + KV_STAGES;  // V stage free: the P V MMAs that read it are done
@@ -81,16 +213,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = (p.T + QT - 1) / QT;
-  // heavy (late) query tiles first
-  const int qi = n_qt - 1 - (int)(blockIdx.x % n_qt);
-  const int bh = blockIdx.x / n_qt;
-  const int h = bh % p.H, b = bh / p.H;
-  const int n_kv = qi + 1;
-  const int row0 = b * p.T;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
@@ -114,29 +240,51 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
+  const int BH = p.B * p.H;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(sQ, &tm_qkv, q_full, h * HD, row0 + qi * QT);
       // K tiles run one tile ahead of V tiles: a K stage is free as soon as its scores are
-      // computed, a V stage only after P V, and the scores of tile j+1 are wanted early
-      for (int j = 0; j <= n_kv; ++j) {
-        if (j < n_kv) {
-          const int s = j % KV_STAGES;
-          const uint32_t ph = (j / KV_STAGES) & 1;
-          if (!mbar_wait_bounded(&k_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
-          mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
-          tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &k_full[s], p.C + h * HD, row0 + j * KT);
+      // computed, a V stage only after P V, and the scores of tile t+1 are wanted early
+      TileIter kt, vt;
+      kt.init(p.T, BH);
+      vt.init(p.T, BH);
+      uint32_t tk = 0, tv = 0, items = 0;
+      bool ok = true;
+      auto load_v = [&]() -> bool {
+        const int h = vt.bh % p.H, row0 = (vt.bh / p.H) * p.T;
+        const int s = tv % KV_STAGES;
+        if (!mbar_wait_bounded(&v_empty[s], ((tv / KV_STAGES) & 1) ^ 1u, abort_flag, p.status, kTimeoutEmpty))
+          return false;
+        mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+        tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &v_full[s], 2 * p.C + h * HD, row0 + vt.j * KT);
+        vt.next_tile(p.T, BH);
+        ++tv;
+        return true;
+      };
+      while (ok && kt.valid) {
+        const int h = kt.bh % p.H, row0 = (kt.bh / p.H) * p.T;
+        if (kt.first()) {
+          if (!mbar_wait_bounded(q_empty, (items & 1u) ^ 1u, abort_flag, p.status, kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(q_full, TILE_BYTES);
+          tma_load_2d(sQ, &tm_qkv, q_full, h * HD, row0 + kt.qi * QT);
+          ++items;
         }
-        if (j > 0) {
-          const int jv = j - 1, s = jv % KV_STAGES;
-          const uint32_t ph = (jv / KV_STAGES) & 1;
-          if (!mbar_wait_bounded(&v_empty[s], ph ^ 1u, abort_flag, p.status, kTimeoutEmpty)) break;
-          mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
-          tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &v_full[s], 2 * p.C + h * HD, row0 + jv * KT);
+        const int s = tk % KV_STAGES;
+        if (!mbar_wait_bounded(&k_empty[s], ((tk / KV_STAGES) & 1) ^ 1u, abort_flag, p.status, kTimeoutEmpty)) {
+          ok = false;
+          break;
         }
+        mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+        tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &k_full[s], p.C + h * HD, row0 + kt.j * KT);
+        kt.next_tile(p.T, BH);
+        ++tk;
+        if (tk >= 2) ok = load_v();  // V(t-1) follows K(t)
       }
+      while (ok && vt.valid) ok = load_v();
       if (*abort_flag) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 2000000ull) {
@@ -149,62 +297,68 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
       constexpr uint32_t idesc_pv = make_idesc_bf16(QT, HD, 0, 1);
       // descriptors are built once; inside the loop an MMA costs one 64-bit add per operand
       const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t p_desc = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
       uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
 #pragma unroll
       for (int s = 0; s < KV_STAGES; ++s) {
         k_desc[s] = make_smem_desc_sw128(smem_u32(sK + s * TILE_BYTES), 16, 1024);
         v_desc[s] = make_smem_desc_sw128(smem_u32(sV + s * TILE_BYTES), 16, 1024);
       }
+      TileIter cur, nxt;
+      cur.init(p.T, BH);
+      nxt.init(p.T, BH);
+      uint32_t q_items = 0;  // items whose Q this warp has started to use
       Z2H_TRACE_DECL(1)
       Z2H_TRACE();
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
-      if (ok) ok = mbar_wait_bounded(&k_full[0], 0, abort_flag, p.status, kTimeoutFull);
-      Z2H_TRACE();
-      if (ok) {
+      // S of flat tile `tn` (the tile `nxt` points at): wait for its operands, issue, commit
+      auto issue_scores = [&](uint32_t tn) -> bool {
+        if (nxt.first()) {
+          if (!mbar_wait_bounded(q_full, q_items & 1u, abort_flag, p.status, kTimeoutFull)) return false;
+          ++q_items;
+        }
+        const int s2 = tn % KV_STAGES;
+        if (!mbar_wait_bounded(&k_full[s2], (tn / KV_STAGES) & 1, abort_flag, p.status, kTimeoutFull))
+          return false;
         tc_fence_after();
+        const uint64_t kd = s2 == 0 ? k_desc[0] : (s2 == 1 ? k_desc[1] : k_desc[2]);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(k_desc[0], k * 32),
+          tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(kd, k * 32),
                         idesc_s, k > 0);
         tc_commit(s_full);
-        tc_commit(&k_empty[0]);
-      }
-      // Per KV tile j: the scores of tile j+1 are issued as soon as the softmax warps hold tile j
-      // in registers, i.e. while they still work on it, and only then P V of tile j. The softmax
+        tc_commit(&k_empty[s2]);
+        if (nxt.last()) tc_commit(q_empty);
+        nxt.next_tile(p.T, BH);
+        return true;
+      };
+      bool ok = cur.valid;
+      if (ok) ok = issue_scores(0);
+      // Per flat tile t: the scores of tile t+1 are issued as soon as the softmax warps hold tile t
+      // in registers, i.e. while they still work on it, and only then P V of tile t. The softmax
       // chain therefore never waits for an MMA of its own tile: S is ready a tile ahead and P V
       // runs behind it.
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (j / KV_STAGES) & 1;
-        if (j + 1 < n_kv) {
-          const int s2 = (j + 1) % KV_STAGES;
-          const uint32_t ph2 = ((j + 1) / KV_STAGES) & 1;
-          if (!mbar_wait_bounded(s_read, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
-          if (!mbar_wait_bounded(&k_full[s2], ph2, abort_flag, p.status, kTimeoutFull)) break;
-          tc_fence_after();
-          const uint64_t kd = s2 == 0 ? k_desc[0] : k_desc[1];
-#pragma unroll
-          for (int k = 0; k < HD / 16; ++k)
-            tc_mma_f16_ss(tmem_base + S_COL, desc_advance(q_desc, k * 32), desc_advance(kd, k * 32),
-                          idesc_s, k > 0);
-          tc_commit(s_full);
-          tc_commit(&k_empty[s2]);
+      for (uint32_t t = 0; ok && cur.valid; ++t) {
+        const int s = t % KV_STAGES;
+        const uint32_t ph = (t / KV_STAGES) & 1;
+        if (nxt.valid) {
+          if (!mbar_wait_bounded(s_read, t & 1, abort_flag, p.status, kTimeoutLocal)) break;
+          Z2H_TRACE();  // the softmax warps hold tile t
+          if (!issue_scores(t + 1)) break;
         }
         Z2H_TRACE();  // scores of the next tile issued
-        if (!mbar_wait_bounded(p_full, j & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        if (!mbar_wait_bounded(p_full, t & 1, abort_flag, p.status, kTimeoutLocal)) break;
         Z2H_TRACE();  // P of this tile is there
         if (!mbar_wait_bounded(&v_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
         tc_fence_after();
-        const uint64_t vd = s == 0 ? v_desc[0] : v_desc[1];
+        const uint64_t vd = s == 0 ? v_desc[0] : (s == 1 ? v_desc[1] : v_desc[2]);
+        const bool fresh = cur.first();
 #pragma unroll
-        for (int k = 0; k < KT / 16; ++k) {
-          tc_mma_f16_ss(tmem_base + PV_COL,
-                        desc_advance(p_desc, (k >> 2) * (QT * 128) + (k & 3) * 32),
-                        desc_advance(vd, k * 2048), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < KT / 16; ++k) {  // keys 16k..16k+15 of P are 8 packed columns
+          tc_mma_f16_ts(tmem_base + PV_COL, tmem_base + P_COL + k * 8, desc_advance(vd, k * 2048),
+                        idesc_pv, (!fresh || k > 0) ? 1u : 0u);
         }
         tc_commit(pv_full);
         tc_commit(&v_empty[s]);
+        cur.next_tile(p.T, BH);
         Z2H_TRACE();  // P V issued
       }
     }
@@ -216,68 +370,65 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
     // maximum grows by more than 2^8 (in the exp2 domain), so O, which accumulates in TMEM
     // across KV tiles, rarely needs rescaling; P stays <= 2^8, well inside bf16 / fp32 range.
     float m_run = -INFINITY, l_run = 0.f;
-    const uint32_t p_row = smem_u32(sP) + r * 128;
     DropoutSpec drop = {};
     unsigned long long drop_row = 0;  // first mask word of this query row
-    if (DROP) {
-      drop = make_dropout_spec(p.seed_ptr, p.site, p.drop_p);
-      drop_row = ((unsigned long long)bh * p.T + (unsigned long long)(qi * QT + r)) *
-                 (unsigned long long)((p.T + 3) / 4);
-    }
+    if (DROP) drop = make_dropout_spec(p.seed_ptr, p.site, p.drop_p);
     bool ok = true;
+    TileIter it;
+    it.init(p.T, BH);
     Z2H_TRACE_DECL(2)
 #define Z2H_CTRACE()                         \
   do {                                       \
     if (warp == 2 && lane == 0) Z2H_TRACE(); \
   } while (0)
     Z2H_CTRACE();
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait_bounded(s_full, j & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+    for (uint32_t t = 0; ok && it.valid; ++t) {
+      const int qi = it.qi, j = it.j;
+      if (it.first()) {
+        m_run = -INFINITY;
+        l_run = 0.f;
+        if (DROP)
+          drop_row = ((unsigned long long)it.bh * p.T + (unsigned long long)(qi * QT + r)) *
+                     (unsigned long long)((p.T + 3) / 4);
+      }
+      Z2H_CTRACE();  // about to wait for the scores
+      if (!mbar_wait_bounded(s_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
       Z2H_CTRACE();  // scores are there
       const bool diag = (j == qi);
-      // the whole score row (128 fp32) comes into registers with one wait
+      // the whole score row (128 fp32) comes into registers with one wait (loading only the
+      // visible chunks would make the register array conditionally defined, which spills)
       uint32_t sv[KT / 32][32];
 #pragma unroll
-      for (int ch = 0; ch < KT / 32; ++ch) tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, sv[ch]);
+      for (int ch = 0; ch < KT / 32; ++ch)
+        tmem_ld_32x32b_x32(t_lane + S_COL + ch * 32, sv[ch]);
       tmem_ld_wait();
       // the score columns may be overwritten with the next tile from here on
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_read);
       Z2H_CTRACE();  // scores in registers
-      float m_new = m_run;
-      if (!diag) {
-        float m0 = m_new, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          m0 = max3(m0, __uint_as_float(sv[0][i]), __uint_as_float(sv[0][i + 1]));
-          m1 = max3(m1, __uint_as_float(sv[1][i]), __uint_as_float(sv[1][i + 1]));
-          m2 = max3(m2, __uint_as_float(sv[2][i]), __uint_as_float(sv[2][i + 1]));
-          m3 = max3(m3, __uint_as_float(sv[3][i]), __uint_as_float(sv[3][i + 1]));
-        }
-        m_new = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      } else {
-#pragma unroll
-        for (int ch = 0; ch < KT / 32; ++ch)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (ch * 32 + i <= r) m_new = fmaxf(m_new, __uint_as_float(sv[ch][i]));
-      }
-      if (j == 0) {
+      const float m_new = diag ? tile_row_max<true>(sv, m_run, quarter, lane)
+                               : tile_row_max<false>(sv, m_run, quarter, lane);
+      Z2H_CTRACE();  // row maximum of this tile known
+      // P V of tile t-1 must be complete before O is rescaled and before P (one buffer in TMEM) is
+      // overwritten. Rescaling is rare (the maximum must grow by 2^8), so the wait normally comes
+      // only after this tile's exponentials, which therefore overlap the previous tile's P V.
+      bool pv_waited = it.first();  // the previous item's epilogue awaited its last P V
+      if (it.first()) {
         m_run = m_new;  // nothing accumulated yet
       } else {
-        // P V of tile j-1 must be complete before O is rescaled and before P is overwritten
-        if (!mbar_wait_bounded(pv_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
         const bool grow = (m_new - m_run) * p.scale_log2 > 8.f;
         if (__any_sync(0xffffffffu, grow)) {
+          if (!mbar_wait_bounded(pv_full, (t - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+            ok = false;
+            break;
+          }
+          pv_waited = true;
+          tc_fence_after();
           const float alpha = grow ? ex2_fast((m_run - m_new) * p.scale_log2) : 1.f;
 #pragma unroll
           for (int q = 0; q < HD / 16; ++q) {
@@ -295,81 +446,62 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
           }
         }
       }
-      Z2H_CTRACE();  // maximum known, previous P V complete
+      Z2H_CTRACE();  // maximum known (and O rescaled if it had to be)
       const float mc = m_run * p.scale_log2;
-      // p = 2^(s * c - m * c), row sum, bf16 P into swizzled shared memory
-      float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-      for (int ch = 0; ch < KT / 32; ++ch) {
-        // 32 columns = four 16-byte chunks of this row inside swizzle atom (ch >> 1)
-        const uint32_t atom = p_row + (ch >> 1) * (QT * 128);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t pk[4];
-          uint32_t mw[2] = {0, 0};
-          if (DROP) {
-            const unsigned long long w0 = drop_row + (unsigned long long)(j * (KT / 4) + ch * 8 + q * 2);
-            mw[0] = dropout_word(drop.seed_lo, drop.seed_hi, w0);
-            mw[1] = dropout_word(drop.seed_lo, drop.seed_hi, w0 + 1);
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = q * 8 + e * 2;
-            float p0 = ex2_fast(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -mc));
-            float p1 = ex2_fast(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -mc));
-            if (diag) {
-              if (ch * 32 + i > r) p0 = 0.f;
-              if (ch * 32 + i + 1 > r) p1 = 0.f;
-            }
-            rs0 += p0;
-            rs1 += p1;
-            if (DROP) {
-              if (!dropout_keep(mw[e >> 1], (e & 1) * 2, drop.threshold)) p0 = 0.f;
-              if (!dropout_keep(mw[e >> 1], (e & 1) * 2 + 1, drop.threshold)) p1 = 0.f;
-            }
-            pk[e] = pack_bf16x2(p0, p1);
-          }
-          const uint32_t chunk = (uint32_t)((ch & 1) * 4 + q) ^ (uint32_t)(r & 7);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(atom + chunk * 16),
-                       "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                       : "memory");
+      // p = 2^(s * c - m * c), row sum, P as packed bf16 pairs into its tensor-memory columns (the
+      // second MMA takes its A operand from there: no shared-memory round trip for P)
+      uint32_t pk[KT / 32][16];
+      const unsigned long long dw0 = DROP ? drop_row + (unsigned long long)(j * (KT / 4)) : 0ull;
+      l_run += diag ? tile_exponentials<true, DROP>(sv, pk, p.scale_log2, mc, quarter, lane, drop, dw0)
+                    : tile_exponentials<false, DROP>(sv, pk, p.scale_log2, mc, quarter, lane, drop, dw0);
+      Z2H_CTRACE();  // exponentials done (in registers)
+      if (!pv_waited) {
+        if (!mbar_wait_bounded(pv_full, (t - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+          ok = false;
+          break;
         }
+        tc_fence_after();
       }
-      l_run += rs0 + rs1;
-      fence_proxy_async();
+#pragma unroll
+      for (int ch = 0; ch < KT / 32; ++ch) tmem_st_32x32b_x16(t_lane + P_COL + ch * 16, pk[ch]);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);  // one arrival per softmax warp
       Z2H_CTRACE();  // P written
-    }
-    if (ok && !mbar_wait_bounded(pv_full, (n_kv - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) ok = false;
-    tc_fence_after();
-    float o[HD];
-    if (ok) {
+      if (it.last()) {
+        // the item is complete once P V of its last tile is: normalise and write the output rows
+        if (!mbar_wait_bounded(pv_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t ov[HD / 32][32];
 #pragma unroll
-      for (int q = 0; q < HD / 32; ++q) {
-        uint32_t ov[32];
-        tmem_ld_32x32b_x32(t_lane + PV_COL + q * 32, ov);
+        for (int q = 0; q < HD / 32; ++q) tmem_ld_32x32b_x32(t_lane + PV_COL + q * 32, ov[q]);
         tmem_ld_wait();
+        tc_fence_before();
+        const int tq = qi * QT + r;
+        if (tq < p.T) {
+          const int h = it.bh % p.H, b = it.bh / p.H;
+          const float inv = DROP ? drop.scale / l_run : 1.f / l_run;
+          __nv_bfloat16* op = p.out + (long long)(b * p.T + tq) * p.C + h * HD;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[q * 32 + i] = __uint_as_float(ov[i]);
+          for (int q = 0; q < HD / 8; ++q) {
+            const uint32_t* o8 = &ov[q >> 2][(q & 3) * 8];
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o8[0]) * inv, __uint_as_float(o8[1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(o8[2]) * inv, __uint_as_float(o8[3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(o8[4]) * inv, __uint_as_float(o8[5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(o8[6]) * inv, __uint_as_float(o8[7]) * inv);
+            *reinterpret_cast<uint4*>(op + q * 8) = u;
+          }
+          if (p.lse != nullptr)
+            p.lse[((long long)b * p.H + h) * p.T + tq] = m_run * p.scale + __logf(l_run);
+        }
+        Z2H_CTRACE();  // output written
       }
-    }
-    const int t = qi * QT + r;
-    if (ok && t < p.T) {
-      const float inv = DROP ? drop.scale / l_run : 1.f / l_run;
-      __nv_bfloat16* op = p.out + (long long)(row0 + t) * p.C + h * HD;
-#pragma unroll
-      for (int q = 0; q < HD / 8; ++q) {
-        uint4 u;
-        u.x = pack_bf16x2(o[q * 8 + 0] * inv, o[q * 8 + 1] * inv);
-        u.y = pack_bf16x2(o[q * 8 + 2] * inv, o[q * 8 + 3] * inv);
-        u.z = pack_bf16x2(o[q * 8 + 4] * inv, o[q * 8 + 5] * inv);
-        u.w = pack_bf16x2(o[q * 8 + 6] * inv, o[q * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(op + q * 8) = u;
-      }
-      if (p.lse != nullptr)
-        p.lse[((long long)b * p.H + h) * p.T + t] = m_run * p.scale + __logf(l_run);
+      it.next_tile(p.T, BH);
     }
   }
 
@@ -408,8 +540,11 @@ int flash_fwd_dropout(const void* qkv, void* out, float* lse, int B, int T, int 
     cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   }
   const int n_qt = (T + QT - 1) / QT;
+  const int items = B * H * n_qt;
+  const int slots = 2 * sm_count_current_device();  // two CTAs per SM
   const cudaError_t err = launch_kernel(drop_p > 0.f ? flash_fwd_kernel<true> : flash_fwd_kernel<false>,
-                                        dim3(B * H * n_qt), dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm, p);
+                                        dim3(items < slots ? items : slots), dim3(NUM_THREADS), SMEM_BYTES,
+                                        stream, true, tm, p);
   return err == cudaSuccess ? 0 : 3;
 }
 

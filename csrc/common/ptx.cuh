@@ -329,6 +329,51 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed fp32 pairs (one instruction, one issue slot, for two lanes of work; sm_100 and later).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+// 2^x for a pair of values on the FMA and integer pipes, no special-function unit: round x to
+// the nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on
+// [-0.5, 0.5] (relative error 7.5e-5, far below bf16 rounding) and add n to the exponent field.
+// x is clamped at -126 from below (smaller values give a denormal-sized result, i.e. ~0); it
+// must be below 128. Used for part of the softmax exponentials, whose other part runs on the
+// special-function unit at the same time: that unit, at 16 results per clock per SM, is what
+// bounds attention at head size 64.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = add2(x, make_float2(kMagic, kMagic));
+  const float2 n = add2(t, make_float2(-kMagic, -kMagic));
+  const float2 r = add2(x, make_float2(-n.x, -n.y));
+  float2 p = fma2(make_float2(0.05517164617776871f, 0.05517164617776871f), r,
+                  make_float2(0.2426111251115799f, 0.2426111251115799f));
+  p = fma2(p, r, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, r, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  // the low mantissa bits of t hold n: shifted into the exponent field and added to p's bits
+  float2 out;
+  out.x = __int_as_float(__float_as_int(t.x) * (1 << 23) + __float_as_int(p.x));
+  out.y = __int_as_float(__float_as_int(t.y) * (1 << 23) + __float_as_int(p.y));
+  return out;
+}
 // Three-input maximum (one instruction on sm_100).
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
