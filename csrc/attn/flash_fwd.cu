@@ -25,6 +25,7 @@
 //              its rows: no TMEM load, no exponentials, zeros into P.
 // TMEM use is 256 columns and shared memory ~113 KiB, so two CTAs share an
 // SM and one CTA's tensor-core work overlaps the other's exponentials.
+#include "../common/checked.cuh"
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
@@ -482,7 +483,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const FwdParams p) 
         tmem_ld_wait();
         tc_fence_before();
         const int tq = qi * QT + r;
-        if (tq < p.T) {
+        if (tq < p.T &&
+            in_bounds((long long)(it.bh / p.H) * p.T + tq, (long long)p.B * p.T, p.status, kSiteFlashFwdOut)) {
           const int h = it.bh % p.H, b = it.bh / p.H;
           const float inv = DROP ? drop.scale / l_run : 1.f / l_run;
           __nv_bfloat16* op = p.out + (long long)(b * p.T + tq) * p.C + h * HD;

@@ -517,9 +517,9 @@ int reduce_bucket_grid(long long n, int max_ctas) {
 }
 
 int reduce_bucket(const BucketArgs& a, cudaStream_t stream) {
-  if (!world_ok(a.rank, a.world) || a.bucket < 0 || a.bucket >= proto::kMaxBuckets) return 1;
-  if ((a.goff % 8) || (a.n % 8) || a.n < 0 || a.dst == nullptr || a.partials == nullptr) return 1;
-  if (reinterpret_cast<uintptr_t>(a.dst) & 15) return 1;
+  if (!world_ok(a.rank, a.world) || a.bucket < 0 || a.bucket >= proto::kMaxBuckets) return -1;
+  if ((a.goff % 8) || (a.n % 8) || a.n < 0 || a.dst == nullptr || a.partials == nullptr) return -1;
+  if (reinterpret_cast<uintptr_t>(a.dst) & 15) return -1;
   const Peers grads = to_peers(a.grads, a.world);
   const Peers pads = to_peers(a.pads, a.world);
   const int grid = reduce_bucket_grid(a.n, a.max_ctas);
@@ -642,8 +642,7 @@ int z2h_reduce_bucket(void* const* grads, void* const* pads, void* grads_mc, int
   a.goff = goff; a.n = n; a.dst = dst; a.one_shot = one_shot;
   a.partials = partials; a.count_sumsq = count_sumsq;
   a.epoch = epoch; a.budget_ns = budget_ns; a.status = status; a.max_ctas = max_ctas;
-  const int rc = z2h::reduce_bucket(a, (cudaStream_t)stream);
-  return rc == 1 ? -1 : rc;
+  return z2h::reduce_bucket(a, (cudaStream_t)stream);
 }
 int z2h_optimizer_phase(void* const* grads, void* const* p16, void* const* pads, void* p16_mc,
                         const float* red, float* p32, float* m, float* v, int rank, int world,

@@ -31,7 +31,7 @@ struct BucketArgs {
   int* status;          // device status word (sticky)
   int max_ctas;         // 0 = fill the device
 };
-// Returns the grid size (>= 1) or a negative error.
+// Returns the grid size (>= 1), -1 for a bad argument or -3 if the launch failed.
 int reduce_bucket(const BucketArgs& a, cudaStream_t stream);
 int reduce_bucket_grid(long long n, int max_ctas);
 

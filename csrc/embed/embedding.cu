@@ -8,6 +8,7 @@
 // Out-of-range token ids are clamped into the table and counted in the status word instead
 // of faulting (the reference kernel bounds-checks ids as well, gpu-mojo/problems/p21/op/
 // embedding.mojo:13-60); the model-level semantics are nn/gpt2/modules.py:104-107.
+#include "../common/checked.cuh"
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "embed.h"
@@ -33,6 +34,9 @@ __global__ void embed_fwd_kernel(const IdxT* __restrict__ idx, const __nv_bfloat
       tok = tok < 0 ? 0 : V - 1;
     }
     const int t = m % T;
+    if (!in_bounds(tok * C + c + 7, (long long)V * C, status, kSiteEmbedTable) ||
+        !in_bounds((long long)m * C + c + 7, (long long)M * C, status, kSiteEmbedOut))
+      continue;
     uint4 a = *reinterpret_cast<const uint4*>(wte + tok * C + c);
     float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z),
            a3 = unpack_bf16x2(a.w);

@@ -1,5 +1,6 @@
 // Parameter block and fused epilogue shared by the one-CTA and the CTA-pair GEMM kernels.
 #pragma once
+#include "../common/checked.cuh"
 #include "../common/ptx.cuh"
 #include "gemm.h"
 
@@ -144,6 +145,7 @@ __device__ __forceinline__ void st_row(void* ptr, const uint32_t (&w)[N_WORDS], 
 template <int EPI, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32_t (&r)[32], long long grow,
                                              int gcol, const float* sbias) {
+  if (!in_bounds_2d(grow, 1, p.M, gcol, 32, p.N, p.status, kSiteGemmRow)) return;
   const bool wide = p.wide != 0;
   float v[32];
 #pragma unroll
@@ -219,9 +221,16 @@ static __device__ __noinline__ void epilogue_row_edge(int epi, int out_fp32, voi
                                                const __nv_bfloat16* residual, long long ldr,
                                                __nv_bfloat16* aux_out, const __nv_bfloat16* aux_in,
                                                long long ldaux, const uint32_t* r, long long grow,
-                                               int gcol, int ncols, const float* sbias) {
+                                               int gcol, int ncols, const float* sbias
+#ifdef Z2H_BOUNDS
+                                               , long long bounds_m, long long bounds_n, int* bounds_status
+#endif
+                                               ) {
 #pragma unroll 1
   for (int j = 0; j < ncols; ++j) {
+#ifdef Z2H_BOUNDS
+    if (!in_bounds_2d(grow, 1, bounds_m, gcol + j, 1, bounds_n, bounds_status, kSiteGemmEdge)) continue;
+#endif
     float v = __uint_as_float(r[j]);
     if (sbias != nullptr) v += sbias[j];
     const long long col = gcol + j;
@@ -261,7 +270,11 @@ __device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uin
 #pragma unroll
       for (int j = 0; j < 32; ++j) tmp[j] = r[c][j];
       epilogue_row_edge(p.epi, p.out_fp32, p.C, p.ldc, p.residual, p.ldr, p.aux_out, p.aux_in, p.ldaux,
-                        tmp, grow, gcol, p.N - gcol, sbias != nullptr ? sbias + c * 32 : nullptr);
+                        tmp, grow, gcol, p.N - gcol, sbias != nullptr ? sbias + c * 32 : nullptr
+#ifdef Z2H_BOUNDS
+                        , p.M, p.N, p.status
+#endif
+                        );
     }
   }
 }
@@ -275,6 +288,7 @@ __device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uin
 __device__ __forceinline__ void epilogue_block_atomic(const KernelParams& p, const uint32_t (&r)[32],
                                                       long long row_base, int gcol, int lane,
                                                       uint32_t stage) {
+  if (!in_bounds_2d(row_base, 32, p.M, gcol, 32, p.N, p.status, kSiteGemmAtomic)) return;
   __syncwarp();  // the previous block's reads of the buffer are done
 #pragma unroll
   for (int c4 = 0; c4 < 8; ++c4) {
@@ -334,7 +348,11 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const uint3
 #pragma unroll
       for (int j = 0; j < 32; ++j) tmp[j] = r[c][j];
       epilogue_row_edge(p.epi, p.out_fp32, p.C, p.ldc, p.residual, p.ldr, p.aux_out, p.aux_in, p.ldaux,
-                        tmp, grow, gcol, min(32, p.N - gcol), sbias != nullptr ? sbias + c * 32 : nullptr);
+                        tmp, grow, gcol, min(32, p.N - gcol), sbias != nullptr ? sbias + c * 32 : nullptr
+#ifdef Z2H_BOUNDS
+                        , p.M, p.N, p.status
+#endif
+                        );
     }
   }
 }

@@ -91,3 +91,33 @@ def test_manual_backprop_matches_autograd(corpus):
     diffs = backprop.check(backprop.init_params(codec.size), X[ix], Y[ix])
     assert set(diffs) >= {"logits", "W1", "C", "bnvar", "fused_ce", "fused_bn"}
     assert max(diffs.values()) < 1e-6, diffs
+
+
+def test_raw_tensor_mlp_with_hand_kept_batchnorm_statistics(corpus):
+    """The bare-tensor MLP (nn/makemore/2_1_mlp.py): running statistics follow the batches with
+    momentum 0.1 and biased variance, evaluation uses them instead of batch statistics, the
+    step-decay schedule divides by the LAST divisor passed, and SGD by hand learns."""
+    from zero_to_hero_b200.makemore import raw_mlp as R
+
+    names, codec = corpus
+    X, Y = build_dataset(names, codec, 4)
+    g = torch.Generator().manual_seed(24)
+    m = R.init_raw_mlp(codec.size, 4, emb_dim=8, hidden=32, generator=g)
+    # one training forward: running stats move a tenth of the way to the batch statistics
+    pre = (m.emb[X[:64]].flatten(1) @ m.w1 + m.b1).detach()
+    R.forward(m, X[:64], True)
+    assert torch.allclose(m.running_mean, 0.1 * pre.mean(0, keepdim=True), atol=1e-6)
+    assert torch.allclose(m.running_var, 0.9 + 0.1 * pre.var(0, keepdim=True, unbiased=False), atol=1e-6)
+    before = (m.running_mean.clone(), m.running_var.clone())
+    a = R.forward(m, X[:7], False)
+    b = R.forward(m, X[:7], False)
+    assert torch.equal(a, b) and torch.equal(m.running_mean, before[0])   # eval: no update, no batch stats
+    assert not torch.allclose(R.forward(m, X[:7], True), a)
+    # schedule: 0.16 until 68 % of the run, then 0.04; later points (same divisor) change nothing
+    assert R.step_decay_lr(0, 1000, 0.16) == 0.16 and R.step_decay_lr(679, 1000, 0.16) == 0.16
+    assert R.step_decay_lr(680, 1000, 0.16) == 0.04 and R.step_decay_lr(999, 1000, 0.16) == 0.04
+    assert R.step_decay_lr(900, 1000, 1.0, (0.5, 0.8), (2, 10)) == 0.1
+    first = R.evaluate_raw_mlp(m, X[:2000], Y[:2000])
+    losses = R.train_raw_mlp(m, X, Y, steps=400, batch_size=64, lr=0.16, generator=g)
+    assert len(losses) == 400 and R.evaluate_raw_mlp(m, X[:2000], Y[:2000]) < first - 0.4
+    assert len(R.sample_raw_mlp(m, codec, 4, 3, g)) == 3

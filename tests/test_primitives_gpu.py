@@ -194,3 +194,17 @@ def test_clusters(P):
         close(P.cluster_reduce(cu(a), 256, 4, dsmem), a.sum().reshape(1), 1e-3)
     b = torch.randn(4096)
     close(P.cluster_reduce(cu(b), 256, 4, True), b.view(4, 1024).sum(1), 1e-3)
+
+
+def test_benchmark_mode_of_the_puzzle_cli(capsys):
+    """`pNN --benchmark`: the size sweeps of the reference's in-puzzle Bench harnesses."""
+    import json
+
+    from zero_to_hero_b200 import puzzles
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    assert puzzles.main(["p32", "--benchmark"]) == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert len(lines) == 4 and all(l["us"] > 0 and l["gbs"] > 0 for l in lines)
+    assert {l["variant"] for l in lines} == {"stride 1", "stride 2"}
+    assert puzzles.main(["p01", "--benchmark"]) == 2      # no sweep for that puzzle

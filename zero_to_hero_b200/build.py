@@ -5,7 +5,9 @@
 micrograd engine, CPU oracles). nvcc cross-compiles without a GPU, so this also is the
 "does it build" check. Objects are cached under `build/` keyed on source mtimes.
 
-Run as `python -m zero_to_hero_b200.build [--force] [--verbose]`.
+Run as `python -m zero_to_hero_b200.build [--force] [--verbose] [--bounds]`. `--bounds` builds the
+self-checking debug variant `libz2h_bounds.so` (-DZ2H_BOUNDS, see csrc/common/checked.cuh), which
+`Z2H_NATIVE_LIB=bounds` selects at run time.
 """
 from __future__ import annotations
 
@@ -57,10 +59,12 @@ def _compile(src: Path, obj: Path, cmd: list[str], verbose: bool) -> tuple[Path,
     return obj, r.stderr
 
 
-def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
-    """Compile all native sources; returns {'cuda': path, 'host': path}."""
+def build_all(force: bool = False, verbose: bool = False, bounds: bool = False) -> dict[str, Path]:
+    """Compile all native sources; returns {'cuda': path, 'host': path}. `bounds`: the CUDA library
+    is built with -DZ2H_BOUNDS into libz2h_bounds.so (the product library is left alone)."""
     nvcc = _nvcc()
-    stamp = _headers_stamp()
+    stamp = _headers_stamp() + ("b" if bounds else "")
+    extra = ["-DZ2H_BOUNDS"] if bounds else []
     LIBDIR.mkdir(parents=True, exist_ok=True)
     cu_srcs = sorted(p for p in CSRC.rglob("*.cu"))
     host_srcs = sorted(p for p in (CSRC / "cpu").rglob("*.cpp"))
@@ -71,7 +75,7 @@ def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
         obj = OBJDIR / rel.with_suffix(f".{stamp}.o")
         cu_objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime_ns < src.stat().st_mtime_ns:
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, obj, cmd))
@@ -88,7 +92,7 @@ def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
             for f in futs:
                 f.result()
     out = {}
-    cuda_lib = LIBDIR / "libz2h.so"
+    cuda_lib = LIBDIR / ("libz2h_bounds.so" if bounds else "libz2h.so")
     if cu_objs and (jobs or force or not cuda_lib.exists()):
         cmd = [nvcc, "-shared", "-o", str(cuda_lib), *map(str, cu_objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
@@ -106,7 +110,11 @@ def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
     return out
 
 
-if __name__ == "__main__":
-    libs = build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+def main() -> None:
+    libs = build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv, bounds="--bounds" in sys.argv)
     for k, v in libs.items():
         print(f"{k}: {v} ({v.stat().st_size if v.exists() else 0} bytes)")
+
+
+if __name__ == "__main__":
+    main()

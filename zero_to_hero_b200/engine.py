@@ -640,7 +640,7 @@ class GPT2TrainEngine:
         if code != 0:
             status.zero_()
             raise RuntimeError(f"z2h kernel reported status {code}: "
-                               f"{_lib.STATUS_NAMES.get(code, '?')}; the last step is invalid")
+                               f"{_lib.describe_status(code)}; the last step is invalid")
         return float(self.loss_host[0])
 
     # ------------------------------------------------------------------ evaluation (forward only)

@@ -1,18 +1,18 @@
 """`python -m zero_to_hero_b200.makemore.cli <model> [--names FILE]` with model in
-bigram-count | bigram-nn | mlp | backprop | wavenet."""
+bigram-count | bigram-nn | mlp-raw | mlp | backprop | wavenet."""
 from __future__ import annotations
 
 import argparse
 
 import torch
 
-from . import backprop, bigram, models
+from . import backprop, bigram, models, raw_mlp
 from .data import CharCodec, build_dataset, load_names, split_names, synthetic_names
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("model", choices=["bigram-count", "bigram-nn", "mlp", "backprop", "wavenet"])
+    ap.add_argument("model", choices=["bigram-count", "bigram-nn", "mlp-raw", "mlp", "backprop", "wavenet"])
     ap.add_argument("--names", default="")
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--seed", type=int, default=42)
@@ -37,6 +37,16 @@ def main(argv=None):
         ix = torch.randint(0, X.shape[0], (32,), generator=g)
         for k, v in backprop.check(backprop.init_params(codec.size), X[ix], Y[ix]).items():
             print(f"{k:16s} max diff {v:.3e}")
+    elif a.model == "mlp-raw":
+        # bare tensors, hand-kept batch-norm running statistics, step-decay learning rate
+        tr, va, _ = split_names(names, a.seed)
+        Xtr, Ytr = build_dataset(tr, codec, 4)
+        Xva, Yva = build_dataset(va, codec, 4)
+        m = raw_mlp.init_raw_mlp(codec.size, 4, generator=g)
+        losses = raw_mlp.train_raw_mlp(m, Xtr, Ytr, a.steps, generator=g)
+        print(f"train loss {losses[0]:.4f} -> {sum(losses[-50:]) / 50:.4f}; "
+              f"val {raw_mlp.evaluate_raw_mlp(m, Xva, Yva):.4f} (running statistics)")
+        print("samples:", raw_mlp.sample_raw_mlp(m, codec, 4, 8, g))
     else:
         block = 4 if a.model == "mlp" else 8
         tr, va, _ = split_names(names, a.seed)

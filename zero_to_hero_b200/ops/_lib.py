@@ -25,10 +25,13 @@ def cuda_lib() -> ctypes.CDLL:
     """The sm_100a kernel library (loads it on first use)."""
     global _cuda_lib
     if _cuda_lib is None:
-        path = _LIBDIR / "libz2h.so"
+        # Z2H_NATIVE_LIB=bounds selects the self-checking debug build (csrc/common/checked.cuh)
+        variant = os.environ.get("Z2H_NATIVE_LIB", "")
+        path = _LIBDIR / ("libz2h_bounds.so" if variant == "bounds" else "libz2h.so")
         if not path.exists():
+            flag = " --bounds" if variant == "bounds" else ""
             raise NativeLibraryMissing(
-                f"{path} is missing: run `python -m zero_to_hero_b200.build` (needs nvcc)")
+                f"{path} is missing: run `python -m zero_to_hero_b200.build{flag}` (needs nvcc)")
         _cuda_lib = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
     return _cuda_lib
 
@@ -77,7 +80,17 @@ STATUS_NAMES = {
     0: "ok", 1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
     3: "timeout waiting for an accumulator", 4: "timeout waiting for accumulator drain",
     5: "timeout waiting for a peer rank", 6: "timeout in an intra-CTA wait", 7: "bad argument",
+    8: "out-of-bounds access caught by the checked build",
 }
+BOUNDS_SITES = {1: "GEMM epilogue row", 2: "GEMM epilogue edge", 3: "GEMM atomic accumulation",
+                4: "embedding table row", 5: "embedding output row", 6: "attention forward output",
+                7: "attention backward output"}
+
+
+def describe_status(s: int) -> str:
+    if (s & 0xFF) == 8:
+        return f"{STATUS_NAMES[8]} (site {s >> 8}: {BOUNDS_SITES.get(s >> 8, '?')})"
+    return STATUS_NAMES.get(s, "?")
 
 
 def check_status(device=None) -> None:
@@ -85,4 +98,4 @@ def check_status(device=None) -> None:
     s = int(status_word(device).item())
     if s != 0:
         status_word(device).zero_()
-        raise RuntimeError(f"z2h kernel reported status {s}: {STATUS_NAMES.get(s, '?')}")
+        raise RuntimeError(f"z2h kernel reported status {s}: {describe_status(s)}")

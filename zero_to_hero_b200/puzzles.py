@@ -5,10 +5,15 @@ checks the result against a CPU oracle, printing `out`, `expected` and a verdict
     python -m zero_to_hero_b200.puzzles p16 --tiled
     python -m zero_to_hero_b200.puzzles p33 --tensor-core
     python -m zero_to_hero_b200.puzzles all
+    python -m zero_to_hero_b200.puzzles p23 --benchmark     # also p24, p30, p31, p32
 
 Counterpart of the reference's `pixi run pNN [-- --flag]` tasks (gpu-mojo/pixi.toml:60-129) and
 the `main()` of every puzzle (e.g. gpu-mojo/problems/p16/p16.mojo:148-231). Flags select the
-variant exactly as there; without a flag the first variant runs.
+variant exactly as there; without a flag the first variant runs. `--benchmark` runs the size
+sweeps of the reference's in-puzzle `Bench` harnesses (gpu-mojo/problems/p23/p23.mojo:474-529,
+p24/p24.mojo:425-511, p30/p30.mojo:381-403, p31/p31.mojo:489-504, p32/p32.mojo) with CUDA-event
+timing (3 warm-ups, median of 20, L2 flushed between launches) and prints one JSON line per
+variant and size with microseconds and achieved GB/s.
 """
 from __future__ import annotations
 
@@ -270,6 +275,61 @@ def p34(f):
     return _check(f"p34 cluster ({f or 'coordination'})", P.cluster_block_sums(cu(a), 256, 4, f == "advanced"), ref, 1e-3)
 
 
+# ------------------------------------------------------------------------------ benchmarks
+def _bench_line(puzzle, variant, n, bytes_moved, fn):
+    import json
+
+    from .utils.kernel_bench import peaks, time_kernel
+    ms = time_kernel(fn, iters=20, warmup=3, flush=True)
+    hbm, _, tag = peaks()
+    gbs = bytes_moved / ms / 1e6
+    print(json.dumps({"puzzle": puzzle, "variant": variant, "n": n, "us": round(ms * 1e3, 2),
+                      "gbs": round(gbs, 1), "frac_hbm": f"{gbs / hbm:.3f} {tag}"}), flush=True)
+
+
+def bench_p23():
+    """Vector add, three kernels, 16 ... 1 Mi elements (and 64 Mi, where DRAM decides)."""
+    for n in [16, 128, 1024, 8192, 65536, 1 << 20, 64 << 20]:
+        a, b = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+        for variant in ("scalar", "tiled", "vectorized"):
+            _bench_line("p23", variant, n, 12 * n, lambda: P.elementwise_add(a, b, variant))
+
+
+def bench_p24():
+    """One dot product per 32 elements: the warp-shuffle kernel against the library expression,
+    1 ... 65536 warps of data."""
+    for warps in [1, 16, 256, 4096, 65536, 1 << 20]:
+        n = warps * 32
+        a, b = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+        _bench_line("p24", "warp_shuffle", n, 8 * n + 4 * warps, lambda: P.warp_dot(a, b))
+        _bench_line("p24", "torch (mul, view, sum)", n, 8 * n + 4 * warps, lambda: (a * b).view(-1, 32).sum(1))
+
+
+def bench_p30():
+    """Coalesced, stride-512 and reversed access over 16 Mi elements."""
+    n = 16 << 20
+    a, b = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+    for mode in ("coalesced", "strided", "reversed"):
+        _bench_line("p30", mode, n, 12 * n, lambda: P.access_pattern_add(a, b, mode))
+
+
+def bench_p31():
+    """SAXPY over 32 Mi elements with 4, 16 and 48 KiB of shared memory per CTA (occupancy)."""
+    n = 32 << 20
+    x, y = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+    for smem in (4096, 16384, 49152):
+        _bench_line("p31", f"smem {smem}", n, 12 * n + 4 * n, lambda: P.occupancy_saxpy(y, x, 2.0, smem))
+
+
+def bench_p32():
+    """Shared-memory stride 1 against stride 2 (two-way bank conflict), 8192 and 16 Mi elements."""
+    for n in (8192, 16 << 20):
+        a = torch.rand(n, device="cuda")
+        for stride in (1, 2):
+            _bench_line("p32", f"stride {stride}", n, 8 * n, lambda: P.bank_conflict(a, stride))
+
+
+BENCHMARKS = {"p23": bench_p23, "p24": bench_p24, "p30": bench_p30, "p31": bench_p31, "p32": bench_p32}
 PUZZLES = {f"p{i:02d}": globals()[f"p{i:02d}"] for i in range(1, 35)}
 FLAGS = ["first-case", "second-case", "third-case", "simple", "block-boundary", "complete", "naive", "single-block",
          "tiled", "compile", "fused", "unfused", "backward", "manual-vectorized", "vectorized", "bulk",
@@ -281,11 +341,20 @@ def main(argv=None) -> int:
     ap.add_argument("puzzle", choices=list(PUZZLES) + ["all"])
     for fl in FLAGS:
         ap.add_argument(f"--{fl}", dest="flag", action="store_const", const=fl)
+    ap.add_argument("--benchmark", action="store_true", help="size sweep with timing (p23, p24, p30, p31, p32)")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("the puzzles need a CUDA device", file=sys.stderr)
         return 2
     names = list(PUZZLES) if a.puzzle == "all" else [a.puzzle]
+    if a.benchmark:
+        todo = [n for n in names if n in BENCHMARKS]
+        if not todo:
+            print(f"no benchmark for {a.puzzle}; available: {sorted(BENCHMARKS)}", file=sys.stderr)
+            return 2
+        for n in todo:
+            BENCHMARKS[n]()
+        return 0
     ok = all(PUZZLES[n](a.flag) for n in names)
     return 0 if ok else 1
 
