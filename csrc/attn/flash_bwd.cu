@@ -340,10 +340,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             const int e4 = q * 2 + e;
             const float4 L = lse4[ch * 8 + e4];
             const float4 D = dlt4[ch * 8 + e4];
-            float p0 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 0]), p.scale_log2, -L.x));
-            float p1 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 1]), p.scale_log2, -L.y));
-            float p2 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 2]), p.scale_log2, -L.z));
-            float p3 = ex2_fast(fmaf(__uint_as_float(sv[ch][e4 * 4 + 3]), p.scale_log2, -L.w));
+            // packed fp32 pairs: one instruction scales and shifts two scores
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            const float2 x01 = fma2(make_float2(__uint_as_float(sv[ch][e4 * 4 + 0]), __uint_as_float(sv[ch][e4 * 4 + 1])),
+                                    sc2, make_float2(-L.x, -L.y));
+            const float2 x23 = fma2(make_float2(__uint_as_float(sv[ch][e4 * 4 + 2]), __uint_as_float(sv[ch][e4 * 4 + 3])),
+                                    sc2, make_float2(-L.z, -L.w));
+            float p0 = ex2_fast(x01.x), p1 = ex2_fast(x01.y), p2 = ex2_fast(x23.x), p3 = ex2_fast(x23.y);
             if (!fast) {
               const int c0 = half * 64 + ch * 32 + e4 * 4;
               if ((diag && c0 + 0 < r) || c0 + 0 >= q_valid) p0 = 0.f;
@@ -366,10 +369,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
               pd2 = k2 ? p2 * drop.scale : 0.f; g2 = k2 ? g2 * drop.scale : 0.f;
               pd3 = k3 ? p3 * drop.scale : 0.f; g3 = k3 ? g3 * drop.scale : 0.f;
             }
-            const float d0 = p0 * (g0 - D.x);
-            const float d1 = p1 * (g1 - D.y);
-            const float d2 = p2 * (g2 - D.z);
-            const float d3 = p3 * (g3 - D.w);
+            const float2 d01 = mul2(make_float2(p0, p1), add2(make_float2(g0, g1), make_float2(-D.x, -D.y)));
+            const float2 d23 = mul2(make_float2(p2, p3), add2(make_float2(g2, g3), make_float2(-D.z, -D.w)));
+            const float d0 = d01.x, d1 = d01.y, d2 = d23.x, d3 = d23.y;
             pt[q * 4 + e * 2 + 0] = pack_bf16x2(pd0, pd1);
             pt[q * 4 + e * 2 + 1] = pack_bf16x2(pd2, pd3);
             dk[e * 2 + 0] = pack_bf16x2(d0, d1);

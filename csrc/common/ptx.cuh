@@ -350,6 +350,16 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 // 2^x for a pair of values on the FMA and integer pipes, no special-function unit: round x to
 // the nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on
 // [-0.5, 0.5] (relative error 7.5e-5, far below bf16 rounding) and add n to the exponent field.

@@ -17,7 +17,9 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    from datetime import timedelta
+    # a rank that fails an assertion leaves; the others must not sit in a collective for long
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
     from zero_to_hero_b200.config import get_preset
     from zero_to_hero_b200.engine import GPT2TrainEngine
     from zero_to_hero_b200.ops import _lib

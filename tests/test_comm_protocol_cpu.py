@@ -126,3 +126,20 @@ def test_ranges_of_all_ranks_partition_every_two_shot_bucket(world):
     # the slices of one bucket are what shard_bounds says
     b0 = buckets[0]
     assert sum(shard_bounds(b0.n, world, r)[1] for r in range(world)) == b0.n
+
+
+def test_bucket_size_grows_until_the_plan_fits_the_signal_pad():
+    """100 layers at one bucket per layer would need more signal slots than a pad has; the
+    communicator doubles the bucket size until the plan fits (same loop as FusedDDP.setup)."""
+    groups, total = _gpt2_like_groups(L=100, per_layer=12 * 64 * 64)
+    size = 12 * 64 * 64 * 4
+    with pytest.raises(ValueError):
+        plan_buckets(total, groups, size, 0)
+    while True:
+        try:
+            buckets = plan_buckets(total, groups, size, 0)
+            break
+        except ValueError:
+            size *= 2
+    assert len(buckets) <= MAX_BUCKETS and sum(b.n for b in buckets) == total
+    assert buckets[0].ready_key < 99     # several layers share the first bucket

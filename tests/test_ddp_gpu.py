@@ -34,7 +34,7 @@ def _run(world, extra_env):
     outs = []
     for p in procs:
         try:
-            out, _ = p.communicate(timeout=600)
+            out, _ = p.communicate(timeout=300)
         except subprocess.TimeoutExpired:
             p.kill()
             out, _ = p.communicate()

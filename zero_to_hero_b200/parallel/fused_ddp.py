@@ -254,7 +254,15 @@ class FusedDDP(PeerComm):
         self.p16_buf = SymmetricBuffer(total, torch.bfloat16, dev, self.group)
         self.g, self.p16 = self.g_buf.tensor, self.p16_buf.tensor
         self.nvls = bool(self._want_nvls and self.g_buf.multicast_ptr and self.p16_buf.multicast_ptr)
-        self.buckets = plan_buckets(total, groups, self.bucket_bytes, self.one_shot_bytes)
+        bucket_bytes = self.bucket_bytes
+        while True:  # a very deep model: merge more layers per bucket until the signal pad has a slot for each
+            try:
+                self.buckets = plan_buckets(total, groups, bucket_bytes, self.one_shot_bytes)
+                break
+            except ValueError as err:
+                if "exceed the limit" not in str(err):
+                    raise
+                bucket_bytes *= 2
         self.ranges, n_state, n_red = plan_ranges(self.buckets, total, self.world_size, self.rank)
         n = max(n_state, 8)
         self.p32_shard = torch.zeros(n, device=dev)

@@ -167,6 +167,49 @@ def bench_adamw(a, dev):
     report(f"gradnorm + adamw n{n} (2 launches)", ms, bytes_=n * (4 * 5 + 4 * 3 + 2.0))
 
 
+def bench_embedding(a, dev):
+    M, C, V, T = a.M, a.C, a.V, a.T
+    idx = torch.randint(0, V, (M,), device=dev)
+    wte = torch.randn(V, C, device=dev).bfloat16()
+    wpe = torch.randn(T, C, device=dev).bfloat16()
+    out = torch.empty(M, C, device=dev, dtype=torch.bfloat16)
+    ms = time_kernel(lambda: N.embed_fwd(idx.view(-1, T), wte, wpe, out, T), a.iters, flush=not a.no_flush)
+    report(f"embed_fwd M{M} C{C} V{V}", ms, bytes_=2.0 * M * C * 2 + T * C * 2)
+    dx = torch.randn(M, C, device=dev).bfloat16()
+    dwte = torch.zeros(V, C, device=dev)
+    dwpe = torch.zeros(T, C, device=dev)
+    ms = time_kernel(lambda: N.embed_bwd(idx.view(-1, T), dx, dwte, dwpe, M // T, T), a.iters,
+                     flush=not a.no_flush)
+    # dx is read by both kernels; the scattered rows are read-modify-written in fp32
+    report(f"embed_bwd M{M} C{C} (2 launches)", ms, bytes_=2.0 * M * C * 2 + 2.0 * M * C * 4 + 2.0 * T * C * 4)
+
+
+def bench_dropout(a, dev):
+    M, C = a.M, a.C
+    x = torch.randn(M, C, device=dev).bfloat16()
+    r = torch.randn(M, C, device=dev).bfloat16()
+    out = torch.empty_like(x)
+    seed = torch.tensor([1234], device=dev, dtype=torch.int64)
+    ms = time_kernel(lambda: N.dropout_apply(x, out, 0.2, seed, 3, residual=r), a.iters, flush=not a.no_flush)
+    report(f"dropout_apply (+residual) M{M} C{C}", ms, bytes_=3.0 * M * C * 2)
+
+
+def bench_colsum(a, dev):
+    M, Nn = a.M, a.N
+    dy = torch.randn(M, Nn, device=dev).bfloat16()
+    db = torch.zeros(Nn, device=dev)
+    ms = time_kernel(lambda: N.colsum_bf16(dy, db), a.iters, flush=not a.no_flush)
+    report(f"colsum_bf16 M{M} N{Nn}", ms, bytes_=1.0 * M * Nn * 2)
+
+
+def bench_sample(a, dev):
+    from ..ops.sampling import sample_topk_native
+    B, V = a.B, a.V
+    logits = torch.randn(B, V, device=dev)
+    ms = time_kernel(lambda: sample_topk_native(logits, 0.8, 50, 7, 0), a.iters, flush=not a.no_flush)
+    report(f"sample_topk B{B} V{V} top-k 50", ms, bytes_=1.0 * B * V * 4)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
@@ -217,6 +260,16 @@ def main():
         bench_ce(a, dev)
     if k in ("adamw", "all"):
         bench_adamw(a, dev)
+    if k in ("embedding", "all"):
+        a.M = 16384 if k == "all" else a.M
+        bench_embedding(a, dev)
+    if k in ("dropout", "all"):
+        bench_dropout(a, dev)
+    if k in ("colsum", "all"):
+        a.N = 3072 if k == "all" else a.N
+        bench_colsum(a, dev)
+    if k in ("sample", "all"):
+        bench_sample(a, dev)
     torch.cuda.synchronize()
     _lib.check_status()
 
