@@ -102,8 +102,11 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
-// scratch layout: [gridDim.x][2][C] fp32 (dw partials, then db partials)
-template <int NVEC, bool HAS_DB>
+// scratch layout: [gridDim.x][NSEG][C] fp32: dw partials, db partials and, with HAS_DXSUM, the
+// column sums of the OUTPUT dx (NSEG = 3). dx is the gradient of the residual stream, i.e. the
+// gradient of the output of the projection that wrote into it, so its column sums are that
+// projection's bias gradient: producing them here saves the separate pass over dx.
+template <int NVEC, bool HAS_DB, bool HAS_DXSUM>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, NVEC <= 4 ? 2 : 1)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
@@ -111,10 +114,12 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
                      __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, int M, int C) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sh[];  // [kWarpsPerCta][2][C]
+  constexpr int NSEG = HAS_DXSUM ? 3 : 2;
+  extern __shared__ float sh[];  // [kWarpsPerCta][NSEG][C]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float dw_acc[NVEC][8];
   float db_acc[HAS_DB ? NVEC : 1][8];
+  float dxs_acc[HAS_DXSUM ? NVEC : 1][8];
   uint4 wraw[NVEC];
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
@@ -125,6 +130,7 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     for (int j = 0; j < 8; ++j) {
       dw_acc[i][j] = 0.f;
       if (HAS_DB) db_acc[i][j] = 0.f;
+      if (HAS_DXSUM) dxs_acc[i][j] = 0.f;
     }
   }
   for (int row = blockIdx.x * kWarpsPerCta + warp; row < M; row += gridDim.x * kWarpsPerCta) {
@@ -199,12 +205,16 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
             o[2 * j + 1] += r.y;
           }
         }
+        if (HAS_DXSUM) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dxs_acc[i][j] += o[j];
+        }
         store8(dx + off + c, o);
       }
     }
   }
   // fold the 8 warps of this CTA, then write one partial row
-  float* my = sh + warp * 2 * C;
+  float* my = sh + warp * NSEG * C;
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int c = (i * 32 + lane) * 8;
@@ -213,15 +223,16 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       for (int j = 0; j < 8; ++j) {
         my[c + j] = dw_acc[i][j];
         my[C + c + j] = HAS_DB ? db_acc[i][j] : 0.f;
+        if (HAS_DXSUM) my[2 * C + c + j] = dxs_acc[i][j];
       }
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+  for (int c = threadIdx.x; c < NSEG * C; c += blockDim.x) {
     float t = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < kWarpsPerCta; ++wi) t += sh[wi * 2 * C + c];
-    scratch[(long long)blockIdx.x * 2 * C + c] = t;
+    for (int wi = 0; wi < kWarpsPerCta; ++wi) t += sh[wi * NSEG * C + c];
+    scratch[(long long)blockIdx.x * NSEG * C + c] = t;
   }
 }
 
@@ -230,24 +241,26 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 // tree in fixed order finishes the sum.
 __global__ void __launch_bounds__(1024)
 layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int num_partials,
-                            float* __restrict__ dw, float* __restrict__ db, int C, int accumulate) {
+                            float* __restrict__ dw, float* __restrict__ db, float* __restrict__ dxsum,
+                            int nseg, int C, int accumulate) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float sh[32][33];
   const int col_in = threadIdx.x & 31, part = threadIdx.x >> 5;
-  const int c2 = blockIdx.x * 32 + col_in;  // column of the [2C] partial row
+  const int c2 = blockIdx.x * 32 + col_in;  // column of the [nseg * C] partial row
   float s = 0.f;
-  if (c2 < 2 * C)
-    for (int p = part; p < num_partials; p += 32) s += scratch[(long long)p * 2 * C + c2];
+  if (c2 < nseg * C)
+    for (int p = part; p < num_partials; p += 32) s += scratch[(long long)p * nseg * C + c2];
   sh[part][col_in] = s;
   __syncthreads();
-  if (part == 0 && c2 < 2 * C) {
+  if (part == 0 && c2 < nseg * C) {
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; ++k) t += sh[k][col_in];
-    float* dst = c2 < C ? dw : db;
-    const int c = c2 < C ? c2 : c2 - C;
-    if (dst != nullptr) dst[c] = accumulate ? dst[c] + t : t;
+    const int seg = c2 / C, c = c2 - seg * C;
+    float* dst = seg == 0 ? dw : (seg == 1 ? db : dxsum);
+    // the column sums of dx always accumulate: they are a bias gradient in the flat buffer
+    if (dst != nullptr) dst[c] = (accumulate || seg == 2) ? dst[c] + t : t;
   }
 }
 
@@ -277,17 +290,30 @@ int layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* m
 int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                   const void* dresid, void* dx, float* dw, float* db, float* scratch, int M, int C,
                   int accumulate, cudaStream_t stream) {
+  return layernorm_bwd_dxsum(dy, x, w, mean, rstd, dresid, dx, dw, db, nullptr, scratch, M, C, accumulate,
+                             stream);
+}
+
+int layernorm_bwd_dxsum(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                        const void* dresid, void* dx, float* dw, float* db, float* dxsum, float* scratch,
+                        int M, int C, int accumulate, cudaStream_t stream) {
   if (C % 8 != 0 || C > 32 * 8 * kMaxVec) return 1;
   if (M <= 0) return 0;
   const int grid = layernorm_bwd_num_partials(M);
-  const size_t smem = (size_t)kWarpsPerCta * 2 * C * sizeof(float);
+  const int nseg = dxsum != nullptr ? 3 : 2;
+  const size_t smem = (size_t)kWarpsPerCta * nseg * C * sizeof(float);
+  if (smem > 227 * 1024) return 1;
 #define Z2H_LN_BWD(NV, DB)                                                                     \
   do {                                                                                         \
-    auto kern = layernorm_bwd_kernel<NV, DB>;                                                  \
+    if (dxsum != nullptr) Z2H_LN_BWD_X(NV, DB, true); else Z2H_LN_BWD_X(NV, DB, false);       \
+  } while (0)
+#define Z2H_LN_BWD_X(NV, DB, DXS)                                                              \
+  do {                                                                                         \
+    auto kern = layernorm_bwd_kernel<NV, DB, DXS>;                                             \
     static std::atomic<unsigned long long> attr_seen{0};                                       \
     if (first_use_on_current_device(attr_seen))                                                \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                           kWarpsPerCta * 2 * 32 * 8 * NV * (int)sizeof(float));               \
+                           kWarpsPerCta * (DXS ? 3 : 2) * 32 * 8 * NV * (int)sizeof(float));   \
     launch_kernel(kern, dim3(grid), dim3(kWarpsPerCta * 32), smem, stream, true,                                            \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, mean, rstd, \
         (const __nv_bfloat16*)dresid, (__nv_bfloat16*)dx, scratch, M, C);                      \
@@ -297,8 +323,9 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
   else if (C <= 1024) { if (has_db) Z2H_LN_BWD(4, true); else Z2H_LN_BWD(4, false); }
   else { if (has_db) Z2H_LN_BWD(8, true); else Z2H_LN_BWD(8, false); }
 #undef Z2H_LN_BWD
-  launch_kernel(layernorm_bwd_reduce_kernel, dim3((2 * C + 31) / 32), dim3(1024), 0, stream, true, scratch, grid, dw, db, C,
-                                                                    accumulate);
+#undef Z2H_LN_BWD_X
+  launch_kernel(layernorm_bwd_reduce_kernel, dim3((nseg * C + 31) / 32), dim3(1024), 0, stream, true, scratch,
+                grid, dw, db, dxsum, nseg, C, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -310,6 +337,13 @@ int z2h_layernorm_fwd(const void* x, const void* w, const void* b, void* y, floa
   return z2h::layernorm_fwd(x, w, b, y, mean, rstd, M, C, eps, (cudaStream_t)stream);
 }
 int z2h_layernorm_bwd_num_partials(int M) { return z2h::layernorm_bwd_num_partials(M); }
+// As z2h_layernorm_bwd; additionally dxsum[C] += column sums of dx (scratch: partials * 3 * C).
+int z2h_layernorm_bwd_dxsum(const void* dy, const void* x, const void* w, const float* mean,
+                            const float* rstd, const void* dresid, void* dx, float* dw, float* db,
+                            float* dxsum, float* scratch, int M, int C, int accumulate, void* stream) {
+  return z2h::layernorm_bwd_dxsum(dy, x, w, mean, rstd, dresid, dx, dw, db, dxsum, scratch, M, C,
+                                  accumulate, (cudaStream_t)stream);
+}
 int z2h_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                       const float* rstd, const void* dresid, void* dx, float* dw, float* db,
                       float* scratch, int M, int C, int accumulate, void* stream) {

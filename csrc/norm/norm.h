@@ -20,4 +20,11 @@ int layernorm_bwd(const void* dy, const void* x, const void* w, const float* mea
                   const void* dresid, void* dx, float* dw, float* db, float* scratch, int M, int C,
                   int accumulate, cudaStream_t stream);
 
+// The same, and in addition dxsum[C] += column sums of dx (always accumulated). dx is the gradient
+// of whatever was added into the residual stream before this LayerNorm, so its column sums are the
+// bias gradient of that projection. scratch must hold num_partials * 3 * C floats here.
+int layernorm_bwd_dxsum(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                        const void* dresid, void* dx, float* dw, float* db, float* dxsum, float* scratch,
+                        int M, int C, int accumulate, cudaStream_t stream);
+
 }  // namespace z2h

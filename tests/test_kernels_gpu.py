@@ -235,6 +235,16 @@ def test_layernorm_fwd_bwd(dev, M, C, has_bias):
     N.layernorm_bwd(dy, x, w, mean, rstd, dres, dx, dw2, torch.zeros(C, device=dev) if has_bias else None,
                     scratch, accumulate=True)
     assert torch.equal(dw, dw2)
+    # fused column sums of the output (the bias gradient of the projection that feeds this
+    # residual stream): accumulated on top of what is there, other outputs unchanged
+    dx3 = torch.empty_like(x)
+    dw3 = torch.zeros(C, device=dev)
+    dxsum = torch.full((C,), 2.0, device=dev)
+    scratch3 = torch.empty(N.layernorm_bwd_num_partials(M) * 3 * C, device=dev)
+    N.layernorm_bwd(dy, x, w, mean, rstd, dres, dx3, dw3, torch.zeros(C, device=dev) if has_bias else None,
+                    scratch3, accumulate=True, dxsum=dxsum)
+    assert torch.equal(dx3, dx) and torch.equal(dw3, dw)
+    assert rel_err(dxsum, 2.0 + (xf.grad + dres.float()).sum(0)) < 1e-3
     status_ok()
 
 

@@ -291,7 +291,7 @@ class GPT2TrainEngine:
         self.d_qkv = buf(M, 3 * C)
         self.dq_accum = buf(N.flash_bwd_dq_elems(B, T, H), dtype=f32)
         self.attn_stats = buf(N.flash_bwd_stats_elems(B, T, H), dtype=f32)
-        self.ln_scratch = buf(N.layernorm_bwd_num_partials(M) * 2 * C, dtype=f32)
+        self.ln_scratch = buf(N.layernorm_bwd_num_partials(M) * 3 * C, dtype=f32)
 
     # ------------------------------------------------------------------ kernels schedule
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, name: str) -> None:
@@ -447,9 +447,14 @@ class GPT2TrainEngine:
         self._side_done = []
         R = [self.d_resid, self.d_resid_alt if self._overlap else self.d_resid]
         cur = 0  # R[cur] holds the residual-stream gradient
+        # Without dropout the gradient of the residual stream IS the gradient of the projection
+        # output that was added into it, so the LayerNorm backward that produces it also sums its
+        # columns into that projection's bias gradient (no separate pass over it).
+        fuse_db = pd == 0.0
         N.layernorm_bwd(self.d_c, self.resid[L], w("transformer.ln_f.weight"), self.stats_f[0],
                         self.stats_f[1], None, R[cur], gw("transformer.ln_f.weight"),
-                        glnb("transformer.ln_f.bias"), self.ln_scratch)
+                        glnb("transformer.ln_f.bias"), self.ln_scratch,
+                        dxsum=gw(f"transformer.h.{L - 1}.mlp.c_proj.bias") if fuse_db and L > 0 else None)
         self._n += 2
         for l in reversed(range(L)):
             p = f"transformer.h.{l}."
@@ -464,7 +469,8 @@ class GPT2TrainEngine:
 
             def wg_mlp_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
-                N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
+                if not fuse_db:
+                    N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
 
             self._on_side(wg_mlp_proj)
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
@@ -479,7 +485,7 @@ class GPT2TrainEngine:
             self._join_side(keep_last=2)  # groups of the previous sub-layer read R[1 - cur]
             N.layernorm_bwd(self.d_c, self.x_mid[l], w(p + "ln_2.weight"), st[2], st[3],
                             R[cur], R[1 - cur], gw(p + "ln_2.weight"), glnb(p + "ln_2.bias"),
-                            self.ln_scratch)
+                            self.ln_scratch, dxsum=gw(p + "attn.c_proj.bias") if fuse_db else None)
             cur = 1 - cur
             # attention
             dy = R[cur]
@@ -490,7 +496,8 @@ class GPT2TrainEngine:
 
             def wg_attn_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
-                N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
+                if not fuse_db:
+                    N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
 
             self._on_side(wg_attn_proj)
             G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
@@ -506,9 +513,12 @@ class GPT2TrainEngine:
             self._join_side(keep_last=2)
             N.layernorm_bwd(self.d_c, self.resid[l], w(p + "ln_1.weight"), st[0], st[1],
                             R[cur], R[1 - cur], gw(p + "ln_1.weight"), glnb(p + "ln_1.bias"),
-                            self.ln_scratch)
+                            self.ln_scratch,
+                            dxsum=gw(f"transformer.h.{l - 1}.mlp.c_proj.bias") if fuse_db and l > 0 else None)
             cur = 1 - cur
-            self._n += 4 + 4 + 2 * 2 + 3  # dgrad GEMMs, column sums, LN bwd (2 kernels each), flash bwd (3)
+            # dgrad GEMMs, column sums (2 of the 4 ride in the LayerNorm backward without dropout),
+            # LN bwd (2 kernels each), flash bwd (3)
+            self._n += 4 + (2 if fuse_db else 4) + 2 * 2 + 3
             if reduce:
                 self._reduce_ready(l)
         self._join_side()

@@ -18,6 +18,7 @@ _sigs = {
     "z2h_layernorm_fwd": [c_void_p] * 6 + [c_int, c_int, c_float, c_void_p],
     "z2h_layernorm_bwd_num_partials": [c_int],
     "z2h_layernorm_bwd": [c_void_p] * 10 + [c_int, c_int, c_int, c_void_p],
+    "z2h_layernorm_bwd_dxsum": [c_void_p] * 11 + [c_int, c_int, c_int, c_void_p],
     "z2h_embed_fwd": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_void_p, c_void_p],
     "z2h_embed_bwd": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -72,12 +73,21 @@ def layernorm_bwd_num_partials(M: int) -> int:
     return _f("z2h_layernorm_bwd_num_partials")(M)
 
 
-def layernorm_bwd(dy, x, w, mean, rstd, dresid, dx, dw, db, scratch, accumulate=True):
+def layernorm_bwd(dy, x, w, mean, rstd, dresid, dx, dw, db, scratch, accumulate=True, dxsum=None):
+    """`dxsum` (fp32 [C], optional): += column sums of the output dx, i.e. the bias gradient of the
+    projection whose output this residual-stream gradient is; scratch then needs 3 * C floats per
+    partial row instead of 2 * C."""
     M, C = x.numel() // x.shape[-1], x.shape[-1]
-    assert scratch.numel() >= layernorm_bwd_num_partials(M) * 2 * C
-    _check(_f("z2h_layernorm_bwd")(ptr(dy), ptr(x), ptr(w), ptr(mean), ptr(rstd), ptr(dresid),
-                                   ptr(dx), ptr(dw), ptr(db), ptr(scratch), M, C, int(accumulate),
-                                   stream_ptr()), "layernorm_bwd")
+    if dxsum is None:
+        assert scratch.numel() >= layernorm_bwd_num_partials(M) * 2 * C
+        _check(_f("z2h_layernorm_bwd")(ptr(dy), ptr(x), ptr(w), ptr(mean), ptr(rstd), ptr(dresid),
+                                       ptr(dx), ptr(dw), ptr(db), ptr(scratch), M, C, int(accumulate),
+                                       stream_ptr()), "layernorm_bwd")
+        return
+    assert scratch.numel() >= layernorm_bwd_num_partials(M) * 3 * C and dxsum.dtype == torch.float32
+    _check(_f("z2h_layernorm_bwd_dxsum")(ptr(dy), ptr(x), ptr(w), ptr(mean), ptr(rstd), ptr(dresid),
+                                         ptr(dx), ptr(dw), ptr(db), ptr(dxsum), ptr(scratch), M, C,
+                                         int(accumulate), stream_ptr()), "layernorm_bwd_dxsum")
 
 
 def embed_fwd(idx, wte, wpe, out, T):
