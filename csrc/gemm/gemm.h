@@ -47,6 +47,10 @@ int gemm_bf16_pair(const GemmArgs& args, cudaStream_t stream);
 // 0: always the one-CTA kernel (128 x 256 tiles); 1: the CTA-pair kernel whenever M >= 256;
 // 2 (default): CTA pairs when the problem has at least one 256 x 256 tile per pair of SMs.
 void gemm_set_algo(int algo);
+// Stream-K with fix-up in the CTA-pair kernel (balanced k-block runs for tile counts that leave a
+// ragged last wave; see gemm_tcgen05_2cta.cu): 0 off (default: it measured slower), 1 on (also
+// Z2H_GEMM_FIXUP=1).
+void gemm_set_fixup(int on);
 int gemm_get_algo();
 
 }  // namespace z2h

@@ -22,8 +22,17 @@ struct KernelParams {
   long long ldaux;
   int* status;
   int wide;      // every row segment the epilogue touches is 32-byte aligned
-  int stream_k;  // work is cut into equal runs of k-blocks instead of whole tiles (atomic-add epilogue only)
+  // 0: whole tiles / split-K slices. 1: stream-K, work cut into equal runs of k-blocks, every
+  // piece added atomically (fp32 output). 2: stream-K with fix-up (any epilogue, CTA-pair kernel):
+  // the piece of a tile that STARTS a worker's run goes to a workspace as fp32, the worker whose run
+  // ENDS in that tile adds it to its own accumulator and runs the epilogue once.
+  int stream_k;
+  float* sk_ws;   // mode 2: [pairs][2 CTAs][8 warps][4 blocks][32 columns][32 lanes] fp32
+  int* sk_flags;  // mode 2: [pairs][2][8], 1 = that warp's piece is in the workspace
 };
+
+constexpr int kSkWarpFloats = 4 * 32 * 32;           // what one epilogue warp parks: 16 KiB
+constexpr int kSkPairFloats = 2 * 8 * kSkWarpFloats;  // 256 KiB per CTA pair
 
 // One unit of work of a CTA (or CTA pair): k-blocks [kb0, kb1) of output tile (mt, nt).
 struct Segment {
@@ -384,6 +393,8 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.split_k = g.split_k < 1 ? 1 : g.split_k;
   p.stream_k = (g.split_k <= 0 && g.epi == kEpiAtomicAdd) ? 1 : 0;
+  p.sk_ws = nullptr;
+  p.sk_flags = nullptr;
   p.epi = g.epi;
   p.out_fp32 = g.out_fp32;
   p.C = g.C; p.ldc = g.ldc;

@@ -326,6 +326,7 @@ extern "C" int z2h_gemm_trace_read(long long* host_out) {
 }
 #endif
 extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }
+extern "C" void z2h_gemm_set_fixup(int on) { z2h::gemm_set_fixup(on); }
 extern "C" int z2h_gemm_get_algo() { return z2h::gemm_get_algo(); }
 extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
                              long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,

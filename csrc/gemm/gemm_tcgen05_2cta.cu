@@ -13,6 +13,9 @@
 // tcgen05.commit arrivals multicast to the same barrier offset in both CTAs. The epilogue
 // warps of both CTAs arrive on the even CTA's "accumulator drained" barrier.
 // Warp roles, epilogues, split-K and operand layouts are those of gemm_tcgen05.cu.
+#include <cstdlib>
+#include <mutex>
+
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
@@ -229,6 +232,58 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tempty_bar[acc]);
       if (warp == 2 && lane == 0) Z2H_TRACE();
+      if (p.stream_k == 2 && !empty_split) {
+        // Stream-K with fix-up. A run of k-blocks may start inside a tile (this worker then has
+        // the tile's tail, the previous worker its head) and may end inside one (this worker has
+        // the head, the next worker the tail). The tail comes first in a run, so it is parked in the
+        // workspace early; the head comes last, so by the time its owner wants the other piece it
+        // has long been there. Both workers map the tile to warps and lanes identically, so a
+        // warp exchanges with the same warp of the neighbouring pair, 128 bytes per instruction.
+        const int slot = ((int)rank * EPI_WARPS + (warp - 2));
+        if (sg.kb0 > 0) {  // tail piece: park it, no epilogue
+          float* ws = p.sk_ws + ((long long)pair * 2 * EPI_WARPS + slot) * gemm_detail::kSkWarpFloats + lane;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(ws + (c * 32 + j) * 32, __uint_as_float(r[c][j]));
+          __threadfence();
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + pair * 2 * EPI_WARPS + slot), "r"(1)
+                         : "memory");
+          continue;
+        }
+        if (sg.kb1 < sched.num_kb) {  // head piece: fetch the neighbour's tail, then the epilogue
+          int* flag = p.sk_flags + (pair + 1) * 2 * EPI_WARPS + slot;
+          int got = 0;
+          if (lane == 0) {
+            const uint64_t t0 = globaltimer_ns();
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(got) : "l"(flag) : "memory");
+              if (got != 0) break;
+              if (*abort_flag != 0 || globaltimer_ns() - t0 > Z2H_WAIT_BUDGET_NS) {
+                *abort_flag = 1;
+                if (p.status != nullptr) atomicCAS(p.status, 0, (int)kTimeoutLocal);
+                break;
+              }
+            }
+          }
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (got == 0) {
+            ok = false;
+            break;
+          }
+          const float* ws =
+              p.sk_ws + ((long long)(pair + 1) * 2 * EPI_WARPS + slot) * gemm_detail::kSkWarpFloats + lane;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              r[c][j] = __float_as_uint(__uint_as_float(r[c][j]) + __ldcg(ws + (c * 32 + j) * 32));
+          __syncwarp();
+          if (lane == 0) *flag = 0;  // consumed: the next launch starts from a clear flag
+        }
+      }
       if (!empty_split)
         gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias, lane,
                                    smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats));
@@ -247,6 +302,47 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+// Workspace of the stream-K fix-up mode: one 256 KiB slot and 16 flags per CTA pair of the current
+// device, allocated on first use (never while the stream is being captured: the first use then
+// simply keeps the whole-tile schedule) and kept until the process ends. The mode is off by default
+// (see the measurements where it is chosen); Z2H_GEMM_FIXUP=1 or gemm_set_fixup(1) turn it on.
+int g_fixup = -1;  // -1: not decided yet (environment), 0 off, 1 on
+bool fixup_enabled() {
+  if (g_fixup < 0) {
+    const char* e = std::getenv("Z2H_GEMM_FIXUP");
+    g_fixup = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return g_fixup == 1;
+}
+
+bool fixup_workspace(cudaStream_t stream, float** ws, int** flags) {
+  static std::mutex mu;
+  static float* ws_dev[64] = {};
+  static int* flags_dev[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ws_dev[dev] == nullptr) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return false;
+    const int pairs = sm_count_current_device() / 2 + 1;
+    float* w = nullptr;
+    int* f = nullptr;
+    if (cudaMalloc(&w, (size_t)pairs * gemm_detail::kSkPairFloats * sizeof(float)) != cudaSuccess) return false;
+    if (cudaMalloc(&f, (size_t)pairs * 2 * EPI_WARPS * sizeof(int)) != cudaSuccess) {
+      cudaFree(w);
+      return false;
+    }
+    cudaMemset(f, 0, (size_t)pairs * 2 * EPI_WARPS * sizeof(int));
+    cudaDeviceSynchronize();
+    ws_dev[dev] = w;
+    flags_dev[dev] = f;
+  }
+  *ws = ws_dev[dev];
+  *flags = flags_dev[dev];
+  return true;
+}
+
 template <int A_MN, int B_MN>
 int launch_pair(const GemmArgs& g, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
@@ -261,13 +357,43 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
   else
     ok = make_tma_2d_bf16(&tmB, g.B, g.K, g.N, g.ldb, BK, 64, kSwizzle128);
   if (!ok) return 2;
-  const KernelParams p = gemm_detail::make_kernel_params(g);
+  KernelParams p = gemm_detail::make_kernel_params(g);
+  const int num_sms_all = sm_count_current_device();
+  {
+    // Stream-K with fix-up for tile counts that leave a ragged last wave (192 tiles on 74 pairs =
+    // 2.6 waves): OFF unless switched on (Z2H_GEMM_FIXUP=1 / gemm_set_fixup). Measured on B200 it
+    // loses everywhere it was tried: M16384 N768 K3072 76.8 us against 72.7 us, N768 K768 35.8 against
+    // 28.7, N3072 K768 79.9 against 67.6, and even the long-K data gradient of the lm_head (K = 50304)
+    // 1133 us against 969 us. Two reasons: every pair parks and fetches one fp32 tile (19 MB each way
+    // per launch), and pairs that walk contiguous runs sit at different k offsets of different tiles, so
+    // the B panel that the whole-tile schedule shares out of L2 (all pairs stream the same k-blocks in
+    // step) is re-read from DRAM. The mode stays as a tested option for shapes with few, very long tiles.
+    int pairs_avail = num_sms_all / 2;
+    if (g.max_ctas > 0 && pairs_avail > g.max_ctas / 2) pairs_avail = g.max_ctas / 2 > 0 ? g.max_ctas / 2 : 1;
+    const long long tiles_sk = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN);
+    const int num_kb = (g.K + BK - 1) / BK;
+    const bool plain = p.stream_k == 0 && p.split_k == 1 && g.epi != kEpiAtomicAdd && g.epi != kEpiAccumulate &&
+                       !g.out_fp32;
+    if (plain && fixup_enabled() && tiles_sk >= pairs_avail && num_kb >= 8) {
+      const double waves = (double)tiles_sk / pairs_avail;
+      const double whole = (double)((tiles_sk + pairs_avail - 1) / pairs_avail);
+      if ((whole - waves) * num_kb >= 48.0) {
+        float* ws = nullptr;
+        int* flags = nullptr;
+        if (fixup_workspace(stream, &ws, &flags)) {
+          p.stream_k = 2;
+          p.sk_ws = ws;
+          p.sk_flags = flags;
+        }
+      }
+    }
+  }
 
   auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
   static std::atomic<unsigned long long> attr_seen{0};
   if (first_use_on_current_device(attr_seen))
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  const int num_sms = sm_count_current_device();
+  const int num_sms = num_sms_all;
   const long long tiles = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) *
                           (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);
   int pairs = num_sms / 2;
@@ -292,6 +418,8 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
 }
 
 }  // namespace
+
+void gemm_set_fixup(int on) { g_fixup = on ? 1 : 0; }
 
 int gemm_bf16_pair(const GemmArgs& g, cudaStream_t stream) {
   if (g.a_mn == 0 && g.b_mn == 0) return launch_pair<0, 0>(g, stream);

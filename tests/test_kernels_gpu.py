@@ -85,6 +85,52 @@ def test_gemm_benchmark_shapes(dev, algo, M, N, K, b_mn):
     assert rel_err(out[rows], ref) < 1e-2
 
 
+@pytest.mark.parametrize("b_mn", [0, 1])
+def test_gemm_stream_k_fixup_matches_whole_tiles(dev, b_mn):
+    """80 tiles of 256 x 256 on 74 CTA pairs (1.08 waves): the balanced schedule cuts tiles between
+    neighbouring pairs and one of them adds the other's piece before the epilogue. Every epilogue,
+    ragged M / N / K, against fp32 and against the whole-tile schedule of the same kernel."""
+    from zero_to_hero_b200.ops import gemm as G
+    M, N, K = 5000, 1000, 520
+    A = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=dev) * 0.5).bfloat16()
+    Bop = B.t().contiguous() if b_mn else B
+    bias = torch.randn(N, device=dev).bfloat16()
+    res = torch.randn(M, N, device=dev).bfloat16()
+    base = A.float() @ B.float().t() + bias.float()
+    outs = {}
+    for fix in (True, False):
+        G.set_fixup(fix)
+        try:
+            o_none = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            G.gemm(A, Bop, o_none, b_mn=bool(b_mn), bias=bias)
+            o_res = torch.empty_like(o_none)
+            G.gemm(A, Bop, o_res, b_mn=bool(b_mn), bias=bias, residual=res, epi=G.EPI_RESIDUAL)
+            o_act, o_pre = torch.empty_like(o_none), torch.empty_like(o_none)
+            G.gemm(A, Bop, o_act, b_mn=bool(b_mn), bias=bias, aux_out=o_pre, epi=G.EPI_GELU)
+            o_gg = torch.empty_like(o_none)
+            G.gemm(A, Bop, o_gg, b_mn=bool(b_mn), aux_in=o_pre, epi=G.EPI_GELU_GRAD)
+            status_ok()
+        finally:
+            G.set_fixup(False)
+        outs[fix] = (o_none, o_res, o_act, o_pre, o_gg)
+        assert rel_err(o_none, base) < 1e-2
+        assert rel_err(o_res, base + res.float()) < 1e-2
+        assert rel_err(o_pre, base) < 1e-2
+        assert rel_err(o_act, F.gelu(o_pre.float(), approximate="tanh")) < 1e-2
+    # same products, same fp32 sums up to the order of two partial sums: bf16 outputs agree closely
+    for a, b in zip(outs[True], outs[False]):
+        assert rel_err(a, b.float()) < 1e-2
+    # and the balanced schedule is reproducible run to run
+    o2 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    G.set_fixup(True)
+    try:
+        G.gemm(A, Bop, o2, b_mn=bool(b_mn), bias=bias)
+    finally:
+        G.set_fixup(False)
+    assert torch.equal(o2, outs[True][0])
+
+
 def test_gemm_epilogues(dev):
     from zero_to_hero_b200.ops import gemm as G
     M, N, K = 520, 776, 264  # tails in every dimension

@@ -69,5 +69,12 @@ def set_algo(algo: int) -> None:
     _lib.cuda_lib().z2h_gemm_set_algo(int(algo))
 
 
+def set_fixup(on: bool) -> None:
+    """Stream-K with fix-up in the CTA-pair kernel (default off: it measured slower on B200): tile
+    counts that leave a ragged last wave are cut into equal runs of k-blocks; a tile shared by two
+    runs is finished by one of them."""
+    _lib.cuda_lib().z2h_gemm_set_fixup(int(bool(on)))
+
+
 def get_algo() -> int:
     return int(_lib.cuda_lib().z2h_gemm_get_algo())
