@@ -3,6 +3,7 @@
 #include "../common/checked.cuh"
 #include "../common/ptx.cuh"
 #include "gemm.h"
+#include <cstdlib>
 
 namespace z2h {
 namespace gemm_detail {
@@ -27,6 +28,11 @@ struct KernelParams {
   // the piece of a tile that STARTS a worker's run goes to a workspace as fp32, the worker whose run
   // ENDS in that tile adds it to its own accumulator and runs the epilogue once.
   int stream_k;
+  // Order in which whole tiles are dealt to the workers that run at the same time: 0 = M fastest
+  // (a wave shares one or two B panels and touches every A panel: right when A fits L2 or N is
+  // wide), 1 = N fastest (a wave holds all N tiles of a few A panels, so A streams from DRAM once:
+  // right for narrow outputs over a long K, e.g. 16384 x 768 with K = 3072, whose A is 100 MB).
+  int raster_n;
   float* sk_ws;   // mode 2: [pairs][2 CTAs][8 warps][4 blocks][32 columns][32 lanes] fp32
   int* sk_flags;  // mode 2: [pairs][2][8], 1 = that warp's piece is in the workspace
 };
@@ -46,13 +52,14 @@ struct Segment {
 //     walked tile by tile, and every piece is added to the output atomically. No worker idles in
 //     a last partial wave, which is what the weight-gradient GEMMs (few tiles, very long K) need.
 struct TileScheduler {
-  int tiles_m, tiles_n, num_kb, kb_per_split, total_items, item, stride, stream_k;
+  int tiles_m, tiles_n, num_kb, kb_per_split, total_items, item, stride, stream_k, raster_n;
   long long u, u_end;
   __device__ TileScheduler(const KernelParams& p, int bm, int bn, int bk, int worker, int workers) {
     tiles_m = (p.M + bm - 1) / bm;
     tiles_n = (p.N + bn - 1) / bn;
     num_kb = (p.K + bk - 1) / bk;
     stream_k = p.stream_k;
+    raster_n = p.raster_n;
     kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
     total_items = tiles_m * tiles_n * p.split_k;
     item = worker;
@@ -75,10 +82,18 @@ struct TileScheduler {
       return true;
     }
     if (item >= total_items) return false;
-    s.mt = item % tiles_m;
-    const int rest = item / tiles_m;
-    s.nt = rest % tiles_n;
-    const int ks = rest / tiles_n;
+    int ks;
+    if (raster_n) {
+      s.nt = item % tiles_n;
+      const int rest = item / tiles_n;
+      s.mt = rest % tiles_m;
+      ks = rest / tiles_m;
+    } else {
+      s.mt = item % tiles_m;
+      const int rest = item / tiles_m;
+      s.nt = rest % tiles_n;
+      ks = rest / tiles_n;
+    }
     s.kb0 = ks * kb_per_split;
     s.kb1 = min(num_kb, s.kb0 + kb_per_split);  // may be empty for the last slices
     item += stride;
@@ -395,6 +410,7 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   p.stream_k = (g.split_k <= 0 && g.epi == kEpiAtomicAdd) ? 1 : 0;
   p.sk_ws = nullptr;
   p.sk_flags = nullptr;
+  p.raster_n = 0;  // the launchers decide (they know their tile shape)
   p.epi = g.epi;
   p.out_fp32 = g.out_fp32;
   p.C = g.C; p.ldc = g.ldc;
@@ -413,6 +429,25 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
              a32(g.aux_in) && (g.ldaux % 16) == 0;
   }
   return p;
+}
+
+// N-fastest tile order when the output is narrower (in tiles) than it is tall and either A is too
+// big to live in L2 across the waves or there are enough N tiles to fill a wave's width: the
+// workers of a wave then cover every N tile of a few row panels, and A is streamed from DRAM once.
+// Measured on B200 (CTA-pair kernel, M = 16384): N768 K3072 71.7 -> 61.4 us, N768 K2304 55.3 -> 49.2,
+// N3072 K768 63.5 -> 61.4, N2304 K768 51.2 -> 50.2; the other way round for N768 K768 (26.7 -> 28.7,
+// A is 25 MB and stays in L2) and for the lm_head (N50304: 942 -> 1057), which keep M fastest.
+// Split-K and stream-K launches keep M fastest as well. Z2H_GEMM_RASTER=m|n forces one order.
+inline int pick_raster_n(const GemmArgs& g, int tm, int tn) {
+  static const int forced = [] {
+    const char* e = std::getenv("Z2H_GEMM_RASTER");
+    return e == nullptr ? -1 : (e[0] == 'n' ? 1 : 0);
+  }();
+  if (forced >= 0) return forced;
+  if (g.split_k != 1) return 0;
+  const int tiles_m = (g.M + tm - 1) / tm, tiles_n = (g.N + tn - 1) / tn;
+  const long long a_bytes = (long long)g.M * g.K * 2;
+  return (tiles_n < tiles_m && (a_bytes >= (48LL << 20) || tiles_n >= 8)) ? 1 : 0;
 }
 
 }  // namespace gemm_detail

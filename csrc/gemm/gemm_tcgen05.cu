@@ -265,7 +265,8 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
     ok = make_tma_2d_bf16(&tmB, g.B, g.K, g.N, g.ldb, BK, 64, kSwizzle128);
   if (!ok) return 2;
 
-  const KernelParams p = gemm_detail::make_kernel_params(g);
+  KernelParams p = gemm_detail::make_kernel_params(g);
+  p.raster_n = gemm_detail::pick_raster_n(g, BM, BN);
 
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
   static std::atomic<unsigned long long> attr_seen{0};

@@ -358,6 +358,7 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
     ok = make_tma_2d_bf16(&tmB, g.B, g.K, g.N, g.ldb, BK, 64, kSwizzle128);
   if (!ok) return 2;
   KernelParams p = gemm_detail::make_kernel_params(g);
+  p.raster_n = gemm_detail::pick_raster_n(g, TM, BN);
   const int num_sms_all = sm_count_current_device();
   {
     // Stream-K with fix-up for tile counts that leave a ragged last wave (192 tiles on 74 pairs =
