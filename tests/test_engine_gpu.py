@@ -284,3 +284,47 @@ def test_checkpoint_restores_dropout_counters_and_rank_state(tmp_path):
     with pytest.raises(ValueError):
         select_rank_state({"world": 2, "per_rank": [1, 2]}, 0, 4)
     assert select_rank_state({"world": 2, "per_rank": ["r0", "r1"]}, 1, 2) == "r1"
+
+
+def test_train_loop_with_eval_hellaswag_checkpoint_and_resume(tmp_path):
+    """The trainer end to end on one GPU: fused engine, forward-only validation, HellaSwag scoring
+    through the engine, JSONL log, a checkpoint, and a resume that continues from it."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import json
+
+    from zero_to_hero_b200.config import get_preset
+    from zero_to_hero_b200.train import train
+
+    g = torch.Generator().manual_seed(0)
+    examples = []
+    for i in range(3):
+        ctx = torch.randint(0, 500, (10 + i,), generator=g).tolist()
+        ends = [torch.randint(0, 500, (4 + j,), generator=g).tolist() for j in range(4)]
+        examples.append({"ctx_tokens": ctx, "ending_tokens": ends, "label": i})
+    hs = tmp_path / "hs.jsonl"
+    hs.write_text("\n".join(json.dumps(e) for e in examples))
+
+    def cfg(steps):
+        c = get_preset("gpt2-tiny")
+        c.model.block_size = 256          # the multiple-choice batches are (4, 256)
+        c.train.micro_batch, c.train.total_batch_tokens = 4, 4 * 256 * 2
+        c.train.steps, c.train.eval_interval, c.train.eval_batches = steps, 1, 1
+        c.train.hellaswag = str(hs)
+        c.train.checkpoint_dir, c.train.checkpoint_interval = str(tmp_path / "ck"), 2
+        c.train.log_jsonl = str(tmp_path / f"log{steps}.jsonl")
+        return c
+
+    out = train(cfg(3))
+    hist = out["history"]
+    assert len(hist) == 3 and all(h["train"] == h["train"] for h in hist)
+    assert all("val" in h and 0.0 <= h["hellaswag"] <= 1.0 for h in hist)
+    assert hist[-1]["train"] < hist[0]["train"] + 0.5
+    ck = tmp_path / "ck" / "step00000002.pt"
+    assert ck.exists()
+    lines = [json.loads(l) for l in (tmp_path / "log3.jsonl").read_text().splitlines()]
+    assert len(lines) == 3 and "tok_s" in lines[0]
+    resumed = train(cfg(4), resume=str(ck))
+    assert [h["step"] for h in resumed["history"]] == [2, 3]
+    # step 2 of the resumed run repeats step 2 of the first run (same weights, moments, data cursor)
+    assert resumed["history"][0]["train"] == pytest.approx(hist[2]["train"], abs=2e-3)
