@@ -42,8 +42,20 @@ constexpr int HD = 64;
 constexpr int TILE_BYTES = TS * HD * 2;  // 16 KiB
 constexpr int PT_BYTES = TS * TS * 2;    // 32 KiB
 constexpr int Q_STAGES = 3;
-constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps
-constexpr int NUM_COMPUTE = 256;
+// Warp 0 loads (TMA), warps 1-3 issue MMAs (one thread each), warps 4-19 compute: four per
+// tensor-memory lane quarter, each taking 32 of the 128 query columns of its 32 key rows.
+//
+// Why three issuing threads. A tcgen05.mma of this kernel's shapes occupies the tensor pipe for
+// 43 cycles (A from tensor memory, N 64), 76 (A from shared memory, N 64) or 107 (N 128): measured
+// with one CTA issuing back to back. Those figures hold only while the issuing warp gets issue
+// slots: with the compute warps of the same scheduler busy, one thread needed 106 cycles per MMA for
+// the dV / dK products instead of 60, and the issuing thread, not the tensor pipe, set the tile
+// period. dV, dK and dQ of a tile are independent, so each has its own issuing thread on its own
+// scheduler and the three streams interleave in the pipe.
+constexpr int NUM_SPECIAL_WARPS = 4;
+constexpr int NUM_COMPUTE = 512;
+constexpr int NUM_THREADS = NUM_SPECIAL_WARPS * 32 + NUM_COMPUTE;
+constexpr int WCOLS = 32;  // query columns per compute warp
 constexpr int TMEM_COLS = 512;
 // S^T and dP^T (fp32, 128 columns each), the dV / dK / dQ accumulators (64 each) and P^T as packed
 // bf16 pairs (64 columns): all 512 columns
@@ -97,7 +109,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   uint64_t* s_read = dq_full + 1;     // the compute warps hold S^T / dP^T of the tile in registers
   uint64_t* dv_done = s_read + 1;     // dV of the tile is complete: P^T may be overwritten
   uint64_t* dq_empty = dv_done + 1;   // the compute warps have read the dQ accumulator
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
+  uint64_t* dk_done = dq_empty + 1;   // dK of the tile is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dk_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,7 +126,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     mbar_init(kv_full, 1);
     for (int s = 0; s < Q_STAGES; ++s) {
       mbar_init(&qdo_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+      mbar_init(&qdo_empty[s], 2);  // the dV thread (after S^T, dP^T, dV) and the dK thread
     }
     mbar_init(st_full, 1);
     mbar_init(pds_full, NUM_COMPUTE / 32);
@@ -121,6 +134,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     mbar_init(s_read, NUM_COMPUTE / 32);
     mbar_init(dv_done, 1);
     mbar_init(dq_empty, NUM_COMPUTE / 32);
+    mbar_init(dk_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -166,12 +180,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t idesc_st = make_idesc_bf16(TS, TS, 0, 0);
       constexpr uint32_t idesc_dvk = make_idesc_bf16(TS, HD, 0, 1);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(TS, HD, 1, 1);
       // descriptors are built once; inside the loop an MMA costs one 64-bit add per operand
       const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
-      const uint64_t dst_desc = make_smem_desc_sw128(smem_u32(sdSt), 16, 1024);
-      const uint64_t dst_mn_desc = make_smem_desc_sw128(smem_u32(sdSt), TS * 128, 1024);
       uint64_t q_desc[Q_STAGES], do_desc[Q_STAGES];
 #pragma unroll
       for (int s = 0; s < Q_STAGES; ++s) {
@@ -181,14 +192,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       auto issue_st = [&](int s) {
         const uint64_t qd = s == 0 ? q_desc[0] : (s == 1 ? q_desc[1] : q_desc[2]);
         const uint64_t dod = s == 0 ? do_desc[0] : (s == 1 ? do_desc[1] : do_desc[2]);
+        // the two products accumulate into different tensor-memory columns: issued alternately,
+        // neither waits for the other's previous step
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
+        for (int k = 0; k < HD / 16; ++k) {
           tc_mma_f16_ss(tmem_base + ST_COL, desc_advance(k_desc, k * 32), desc_advance(qd, k * 32),
                         idesc_st, k > 0);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
           tc_mma_f16_ss(tmem_base + DPT_COL, desc_advance(v_desc, k * 32), desc_advance(dod, k * 32),
                         idesc_st, k > 0);
+        }
         tc_commit(st_full);
       };
       Z2H_TRACE_DECL(1)
@@ -205,13 +217,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       //   S^T, dP^T of it+1   as soon as the compute warps hold the scores of tile `it` in
       //                       registers (s_read), i.e. while they still work on tile `it`; three
       //                       Q / dO stages keep the operands of tiles it+1 and it+2 in flight
-      //   dV += P^T dO        once P^T (tensor memory) and dS^T (shared memory) are written;
-      //                       the A operand comes straight from tensor memory
-      //   dK += dS^T Q        last reader of the Q / dO stage, which is handed back here
-      //   dQ  = dS K          after the compute warps have read the previous tile's dQ
+      //   dV += P^T dO        once P^T (tensor memory) is written; the A operand comes straight
+      //                       from tensor memory
+      // (dK += dS^T Q and dQ = dS K are issued by warps 2 and 3)
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % Q_STAGES;
-        const uint32_t pb = (it & 1) * PT_BYTES;
         if (it + 1 < n_iter) {
           const int s2 = (it + 1) % Q_STAGES;
           const uint32_t ph2 = ((it + 1) / Q_STAGES) & 1;
@@ -224,20 +234,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
         Z2H_TRACE();
         tc_fence_after();
-        const uint64_t qd = s == 0 ? q_desc[0] : (s == 1 ? q_desc[1] : q_desc[2]);
         const uint64_t dod = s == 0 ? do_desc[0] : (s == 1 ? do_desc[1] : do_desc[2]);
 #pragma unroll
-        for (int k = 0; k < TS / 16; ++k)  // queries 16k..16k+15 of P^T are 8 packed columns
+        for (int k = 0; k < TS / 16; ++k) {  // queries 16k..16k+15 of P^T are 8 packed columns
           tc_mma_f16_ts(tmem_base + DV_COL, tmem_base + PT_COL + k * 8, desc_advance(dod, k * 2048),
                         idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
+        }
         tc_commit(dv_done);
+        tc_commit(&qdo_empty[s]);  // covers this thread's earlier reads of the stage (S^T, dP^T) too
+        Z2H_TRACE();
+      }
+    }
+  } else if (warp == 2) {
+    // dK += dS^T Q: A is dS^T of the tile (shared memory, K-major), B the Q tile (MN-major)
+    if (lane == 0) {
+      constexpr uint32_t idesc_dvk = make_idesc_bf16(TS, HD, 0, 1);
+      const uint64_t dst_desc = make_smem_desc_sw128(smem_u32(sdSt), 16, 1024);
+      uint64_t q_desc[Q_STAGES];
+#pragma unroll
+      for (int s = 0; s < Q_STAGES; ++s) q_desc[s] = make_smem_desc_sw128(smem_u32(sQ + s * TILE_BYTES), 16, 1024);
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % Q_STAGES;
+        const uint32_t pb = (it & 1) * PT_BYTES;
+        if (!mbar_wait_bounded(&qdo_full[s], (it / Q_STAGES) & 1, abort_flag, p.status, kTimeoutFull)) break;
+        if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
+        tc_fence_after();
+        const uint64_t qd = s == 0 ? q_desc[0] : (s == 1 ? q_desc[1] : q_desc[2]);
 #pragma unroll
         for (int k = 0; k < TS / 16; ++k) {
           const uint32_t a_off = pb + (k >> 2) * (TS * 128) + (k & 3) * 32;
           tc_mma_f16_ss(tmem_base + DK_COL, desc_advance(dst_desc, a_off), desc_advance(qd, k * 2048),
                         idesc_dvk, (it > 0 || k > 0) ? 1u : 0u);
         }
+        tc_commit(dk_done);
         tc_commit(&qdo_empty[s]);
+      }
+    }
+  } else if (warp == 3) {
+    // dQ = dS K: A is dS read MN-major from the dS^T tile, B the K tile (MN-major); the compute warps
+    // must have read the previous tile's dQ out of the accumulator first
+    if (lane == 0) {
+      constexpr uint32_t idesc_dq = make_idesc_bf16(TS, HD, 1, 1);
+      const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dst_mn_desc = make_smem_desc_sw128(smem_u32(sdSt), TS * 128, 1024);
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFull);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t pb = (it & 1) * PT_BYTES;
+        if (!mbar_wait_bounded(pds_full, it & 1, abort_flag, p.status, kTimeoutLocal)) break;
         if (it > 0 && !mbar_wait_bounded(dq_empty, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
 #pragma unroll
@@ -246,14 +289,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
                         desc_advance(k_desc, k * 2048), idesc_dq, k > 0);
         }
         tc_commit(dq_full);
-        Z2H_TRACE();
       }
     }
   } else {
-    // Two warps share each TMEM lane quarter: warp (2 + q) takes query columns 0..63 of a key
-    // row, warp (6 + q) columns 64..127, so every SM sub-partition has two compute warps.
+    // Four warps share each TMEM lane quarter: warp (4 + q + 4 * part) takes query columns
+    // part*32 .. part*32+31 of a key row, so every SM sub-partition has four compute warps.
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - NUM_SPECIAL_WARPS) >> 2;   // 0..3: which 32 query columns
+    const int half = part >> 1;         // which 64-column swizzle atom of dS^T
+    const int sub = part & 1;           // which 32-column half of that atom
     const int r = quarter * 32 + lane;  // key row (S^T, dV, dK) or query row (dQ) == TMEM lane
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t dst_row = smem_u32(sdSt) + half * (TS * 128) + r * 128;
@@ -265,16 +309,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       // blocked layout [row / 32][head][16-byte column group][row % 32]: the 32 lanes of a warp
       // (32 consecutive rows) hit 512 contiguous bytes per instruction instead of 32 rows
       const long long g = (long long)row0 + tq;
-      float* dq_row = p.dq_accum + ((((g >> 5) * p.H + h) * 16 + half * 8) * 32 + (g & 31)) * 4;
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(t_lane + DQ_COL + half * 32, v);
+      float* dq_row = p.dq_accum + ((((g >> 5) * p.H + h) * 16 + part * 4) * 32 + (g & 31)) * 4;
+      uint32_t v[16];
+      tmem_ld_32x32b_x16(t_lane + DQ_COL + part * 16, v);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);
       if (tq < p.T) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 4; ++q) {
           asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + q * 128),
                        "f"(__uint_as_float(v[q * 4 + 0])), "f"(__uint_as_float(v[q * 4 + 1])),
                        "f"(__uint_as_float(v[q * 4 + 2])), "f"(__uint_as_float(v[q * 4 + 3]))
@@ -291,7 +335,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     Z2H_TRACE_DECL(2)
 #define Z2H_CTRACE()                      \
   do {                                    \
-    if (warp == 2 && lane == 0) Z2H_TRACE(); \
+    if (warp == NUM_SPECIAL_WARPS && lane == 0) Z2H_TRACE(); \
   } while (0)
     Z2H_CTRACE();
     for (int it = 0; it < n_iter; ++it) {
@@ -317,20 +361,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       const bool diag = (i == j);
       const int q_valid = p.T - i * TS;  // columns >= q_valid are past the end of the sequence
       const bool fast = !diag && q_valid >= TS;  // no masking anywhere in this tile
-      const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * TS + half * 64);
-      const float4* dlt4 = reinterpret_cast<const float4*>(sDelta + s * TS + half * 64);
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64, sv[0]);
-      tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64, dv[0]);
-      tmem_ld_32x32b_x32(t_lane + ST_COL + half * 64 + 32, sv[1]);
-      tmem_ld_32x32b_x32(t_lane + DPT_COL + half * 64 + 32, dv[1]);
+      const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * TS + part * WCOLS);
+      const float4* dlt4 = reinterpret_cast<const float4*>(sDelta + s * TS + part * WCOLS);
+      uint32_t sv[1][32], dv[1][32];
+      tmem_ld_32x32b_x32(t_lane + ST_COL + part * WCOLS, sv[0]);
+      tmem_ld_32x32b_x32(t_lane + DPT_COL + part * WCOLS, dv[0]);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_read);  // S^T / dP^T columns may be overwritten from here on
       Z2H_CTRACE();  // scores in registers
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      for (int ch = 0; ch < 1; ++ch) {
         uint32_t pt[16];  // P^T of these 32 queries, packed bf16 pairs
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -348,7 +390,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
                                     sc2, make_float2(-L.z, -L.w));
             float p0 = ex2_fast(x01.x), p1 = ex2_fast(x01.y), p2 = ex2_fast(x23.x), p3 = ex2_fast(x23.y);
             if (!fast) {
-              const int c0 = half * 64 + ch * 32 + e4 * 4;
+              const int c0 = part * WCOLS + e4 * 4;
               if ((diag && c0 + 0 < r) || c0 + 0 >= q_valid) p0 = 0.f;
               if ((diag && c0 + 1 < r) || c0 + 1 >= q_valid) p1 = 0.f;
               if ((diag && c0 + 2 < r) || c0 + 2 >= q_valid) p2 = 0.f;
@@ -359,7 +401,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             float pd0 = p0, pd1 = p1, pd2 = p2, pd3 = p3;  // what multiplied V in the forward pass
             if (DROP) {
               // this thread's key is fixed; the four queries of this step are consecutive rows
-              const unsigned long long w0 = drop_q0 + (unsigned long long)(half * 64 + ch * 32 + e4 * 4) * drop_wpr;
+              const unsigned long long w0 = drop_q0 + (unsigned long long)(part * WCOLS + e4 * 4) * drop_wpr;
               const bool k0 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0), drop_byte, drop.threshold);
               const bool k1 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0 + drop_wpr), drop_byte, drop.threshold);
               const bool k2 = dropout_keep(dropout_word(drop.seed_lo, drop.seed_hi, w0 + 2 * drop_wpr), drop_byte, drop.threshold);
@@ -378,26 +420,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             dk[e * 2 + 1] = pack_bf16x2(d2, d3);
           }
           // 8 columns = one 16-byte chunk of this row inside swizzle atom `half`
-          const uint32_t chunk = ((uint32_t)(ch * 4 + q) ^ (uint32_t)(r & 7)) * 16;
+          const uint32_t chunk = ((uint32_t)(sub * 4 + q) ^ (uint32_t)(r & 7)) * 16;
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + pb + chunk), "r"(dk[0]),
                        "r"(dk[1]), "r"(dk[2]), "r"(dk[3])
                        : "memory");
         }
         // P^T goes to its tensor-memory columns (the dV product reads its A operand there); the
         // previous tile's dV must have finished reading them
-        if (ch == 0 && it > 0 &&
-            !mbar_wait_bounded(dv_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        if (it > 0 && !mbar_wait_bounded(dv_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
           ok = false;
           break;
         }
-        tmem_st_32x32b_x16(t_lane + PT_COL + half * 32 + ch * 16, pt);
+        tmem_st_32x32b_x16(t_lane + PT_COL + part * 16, pt);
       }
       if (!ok) break;
       tmem_st_wait();
       Z2H_CTRACE();  // P^T / dS^T written
       // The products of tile it-1 must have completed before this warp signals tile `it`: a later
       // wait could otherwise see the barrier two phases ahead and mistake the parity.
-      if (it > 0 && !mbar_wait_bounded(dq_full, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+      if (it > 0 && !(mbar_wait_bounded(dq_full, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull) &&
+                      mbar_wait_bounded(dk_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull))) {
         ok = false;
         break;
       }
@@ -413,18 +455,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     if (ok && n_iter > 0) {
       ok = mbar_wait_bounded(dq_full, (n_iter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
       if (ok) drain_dq(n_iter - 1);
+      // dV and dK of this KV tile are complete once their last commits have fired
+      if (ok) ok = mbar_wait_bounded(dv_done, (n_iter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
+      if (ok) ok = mbar_wait_bounded(dk_done, (n_iter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
+      if (ok) tc_fence_after();
     }
-    // dV and dK of this KV tile are complete once the last dq_full has fired
     const int tk = j * TS + r;
     if (ok) {
-      __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD + half * 32;
+      __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD + part * 16;
       __nv_bfloat16* dv_row = dk_row + p.C;
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(t_lane + DV_COL + half * 32, v);
+      uint32_t v[16];
+      tmem_ld_32x32b_x16(t_lane + DV_COL + part * 16, v);
       tmem_ld_wait();
       if (tk < p.T) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
           uint4 u;
           u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
           u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
@@ -433,11 +478,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           *reinterpret_cast<uint4*>(dv_row + q * 8) = u;
         }
       }
-      tmem_ld_32x32b_x32(t_lane + DK_COL + half * 32, v);
+      tmem_ld_32x32b_x16(t_lane + DK_COL + part * 16, v);
       tmem_ld_wait();
       if (tk < p.T) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
           uint4 u;
           u.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]) * p.scale, __uint_as_float(v[q * 8 + 1]) * p.scale);
           u.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]) * p.scale, __uint_as_float(v[q * 8 + 3]) * p.scale);

@@ -34,6 +34,10 @@ struct GemmArgs {
   const void* aux_in;     // bf16 [M, ldaux]
   long long ldaux;
   int* status;            // device status word (0 == ok), may be null
+  // fp32 [N] or null: the column sums of C (as stored, i.e. rounded to bf16) are ADDED to it, which
+  // makes the bias gradient of the layer below a by-product of the GEMM that produces that layer's
+  // output gradient. Needs a bf16 output, split_k == 1, M % 32 == 0 and N % 32 == 0.
+  void* colsum;
   int max_ctas;           // 0 = one CTA per SM
 };
 

@@ -22,6 +22,7 @@ struct KernelParams {
   const __nv_bfloat16* aux_in;
   long long ldaux;
   int* status;
+  float* colsum;  // fp32 [N] or null: column sums of the (bf16-rounded) output are added here
   int wide;      // every row segment the epilogue touches is 32-byte aligned
   // 0: whole tiles / split-K slices. 1: stream-K, work cut into equal runs of k-blocks, every
   // piece added atomically (fp32 output). 2: stream-K with fix-up (any epilogue, CTA-pair kernel):
@@ -163,6 +164,24 @@ __device__ __forceinline__ void st_row(void* ptr, const uint32_t (&w)[N_WORDS], 
   }
 }
 
+// Column sums of a 32 x 32 block held one row per lane (v[j] = column j of this lane's row): a
+// butterfly in which every step halves the columns a lane keeps and doubles the rows they cover.
+// After the five steps lane l holds, in v[0], the sum of column l over the warp's 32 rows:
+// 31 shuffles per block instead of 32 x 5.
+__device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int j = 0; j < s; ++j) {
+      const float send = upper ? v[j] : v[j + s];
+      const float keep = upper ? v[j + s] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+    }
+  }
+  return v[0];
+}
+
 // Epilogue of 32 consecutive columns of one output row, all of which exist; one instantiation
 // per epilogue kind and output type keeps each kernel's hot path short.
 //   r: the accumulator values (fp32 bit patterns); sbias: bias of these columns in shared memory.
@@ -235,6 +254,18 @@ __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32
 #pragma unroll
     for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
     st_row(reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + gcol, w, wide);
+    if (p.colsum != nullptr) {
+      // bias gradient of the layer whose output gradient this GEMM produces: sum what was stored
+      // (the rounded values, as a separate pass over C would). The launcher admits this only when
+      // M is a multiple of 32, so all 32 lanes of the warp are here.
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        v[2 * j] = f.x; v[2 * j + 1] = f.y;
+      }
+      const float sum = warp_column_sums(v, (int)(threadIdx.x & 31));
+      asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.colsum + gcol + (threadIdx.x & 31)), "f"(sum) : "memory");
+    }
   }
 }
 
@@ -421,6 +452,7 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   p.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in);
   p.ldaux = g.ldaux;
   p.status = g.status;
+  p.colsum = reinterpret_cast<float*>(g.colsum);
   {
     // 32-byte vectors need 32-byte aligned bases and pitches (bf16: 16 elements, fp32: 8)
     auto a32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };

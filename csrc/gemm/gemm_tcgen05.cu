@@ -302,6 +302,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
   if (reinterpret_cast<uintptr_t>(g.bias) & 7) return 1;
+  if (g.colsum != nullptr && (g.out_fp32 || g.split_k != 1 || (g.M % 32) || (g.N % 32) ||
+                              (reinterpret_cast<uintptr_t>(g.colsum) & 3)))
+    return 1;
   if ((reinterpret_cast<uintptr_t>(g.residual) & 15) || (reinterpret_cast<uintptr_t>(g.aux_out) & 15) ||
       (reinterpret_cast<uintptr_t>(g.aux_in) & 15))
     return 1;
@@ -329,11 +332,12 @@ extern "C" int z2h_gemm_trace_read(long long* host_out) {
 extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }
 extern "C" void z2h_gemm_set_fixup(int on) { z2h::gemm_set_fixup(on); }
 extern "C" int z2h_gemm_get_algo() { return z2h::gemm_get_algo(); }
-extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
-                             long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
-                             int epi, int split_k, const void* bias, const void* residual,
-                             long long ldr, void* aux_out, const void* aux_in, long long ldaux,
-                             int* status, int max_ctas, void* stream) {
+// z2h_gemm_bf16 plus the column-sum by-product (see GemmArgs::colsum).
+extern "C" int z2h_gemm_bf16_colsum(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                                    long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                                    int epi, int split_k, const void* bias, const void* residual,
+                                    long long ldr, void* aux_out, const void* aux_in, long long ldaux,
+                                    int* status, int max_ctas, void* colsum, void* stream) {
   z2h::GemmArgs g;
   g.A = A; g.a_mn = a_mn; g.lda = lda;
   g.B = B; g.b_mn = b_mn; g.ldb = ldb;
@@ -343,5 +347,14 @@ extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   g.bias = bias; g.residual = residual; g.ldr = ldr;
   g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
   g.status = status; g.max_ctas = max_ctas;
+  g.colsum = colsum;
   return z2h::gemm_bf16(g, reinterpret_cast<cudaStream_t>(stream));
+}
+extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                             long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                             int epi, int split_k, const void* bias, const void* residual,
+                             long long ldr, void* aux_out, const void* aux_in, long long ldaux,
+                             int* status, int max_ctas, void* stream) {
+  return z2h_gemm_bf16_colsum(A, a_mn, lda, B, b_mn, ldb, C, ldc, out_fp32, M, N, K, epi, split_k, bias,
+                              residual, ldr, aux_out, aux_in, ldaux, status, max_ctas, nullptr, stream);
 }

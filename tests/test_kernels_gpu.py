@@ -163,6 +163,37 @@ def test_gemm_epilogues(dev):
     status_ok()
 
 
+@pytest.mark.parametrize("algo", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(512, 768, 264), (16384, 3072, 768), (2080, 352, 96)])
+def test_gemm_column_sums_of_the_output(dev, algo, M, N, K):
+    """The epilogue's by-product: the column sums of C as stored (bf16) are added to an fp32
+    vector; against a separate fp32 sum over the rows of the same C."""
+    from zero_to_hero_b200.ops import gemm as G
+    torch.manual_seed(M + N)
+    A = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    B = (torch.randn(K, N, device=dev) * 0.5).bfloat16()
+    pre = torch.randn(M, N, device=dev).bfloat16()
+    G.set_algo(algo)
+    try:
+        for epi, kw in ((G.EPI_GELU_GRAD, dict(aux_in=pre)), (G.EPI_NONE, {})):
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            start = torch.randn(N, device=dev)
+            acc = start.clone()
+            G.gemm(A, B, out, b_mn=True, epi=epi, colsum=acc, **kw)
+            ref = torch.empty_like(out)
+            G.gemm(A, B, ref, b_mn=True, epi=epi, **kw)
+            assert torch.equal(out, ref)  # the by-product leaves C alone
+            want = start + out.float().sum(0)
+            assert (acc - want).abs().max().item() <= 1e-4 * out.float().abs().sum(0).max().item() + 1e-4
+        # a shape whose rows do not fill whole warps is refused, not computed wrongly
+        with pytest.raises(RuntimeError):
+            G.gemm(A[:40], B, torch.empty(40, N, device=dev, dtype=torch.bfloat16), b_mn=True,
+                   colsum=torch.zeros(N, device=dev))
+    finally:
+        G.set_algo(2)
+    status_ok()
+
+
 def test_gemm_deterministic_without_atomics(dev):
     from zero_to_hero_b200.ops import gemm as G
     A = torch.randn(1024, 768, device=dev).bfloat16()

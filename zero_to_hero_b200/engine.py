@@ -473,12 +473,17 @@ class GPT2TrainEngine:
                     N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
 
             self._on_side(wg_mlp_proj)
+            # the c_fc bias gradient is the column sum of d_4c: a by-product of this GEMM's epilogue
+            # (the epilogue's column butterfly needs whole warps of rows)
+            fc_db_in_gemm = self.M % 32 == 0
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
-                   aux_in=self.pre[l], epi=G.EPI_GELU_GRAD)
+                   aux_in=self.pre[l], epi=G.EPI_GELU_GRAD,
+                   colsum=gw(p + "mlp.c_fc.bias") if fc_db_in_gemm else None)
 
-            def wg_mlp_fc(l=l, p=p):
+            def wg_mlp_fc(l=l, p=p, fc_db_in_gemm=fc_db_in_gemm):
                 self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
-                N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
+                if not fc_db_in_gemm:
+                    N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
 
             self._on_side(wg_mlp_fc)
             G.gemm(self.d_4c, w(p + "mlp.c_fc.weight"), self.d_c, b_mn=True)

@@ -16,8 +16,8 @@ def _fn():
     global _configured
     lib = _lib.cuda_lib()
     if not _configured:
-        lib.z2h_gemm_bf16.restype = ctypes.c_int
-        lib.z2h_gemm_bf16.argtypes = [
+        lib.z2h_gemm_bf16_colsum.restype = ctypes.c_int
+        lib.z2h_gemm_bf16_colsum.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
             ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
             ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
@@ -25,16 +25,17 @@ def _fn():
             ctypes.c_int, ctypes.c_int,
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
-            ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
         ]
         _configured = True
-    return lib.z2h_gemm_bf16
+    return lib.z2h_gemm_bf16_colsum
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False,
          b_mn: bool = False, epi: int = EPI_NONE, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, aux_out: torch.Tensor | None = None,
-         aux_in: torch.Tensor | None = None, split_k: int = 1, max_ctas: int = 0) -> torch.Tensor:
+         aux_in: torch.Tensor | None = None, split_k: int = 1, max_ctas: int = 0,
+         colsum: torch.Tensor | None = None) -> torch.Tensor:
     """out[M,N] (op)= A · Bᵀ on the tensor cores.
 
     `a` is [M,K] (or [K,M] when `a_mn`), `b` is [N,K] (or [K,N] when `b_mn`); both bf16 with a
@@ -42,6 +43,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
     `split_k` > 1 cuts K into that many slices; 0 selects the stream-K schedule (one equal run of
     k-blocks per SM); both need `epi=EPI_ATOMIC_ADD` and an fp32 `out` that already holds the
     value to add to.
+    `colsum` (fp32 [N]): the column sums of `out` as stored are ADDED to it by the epilogue, i.e. the
+    bias gradient of the layer whose output gradient this GEMM produces comes for free; needs a bf16
+    `out`, `split_k == 1` and M, N multiples of 32.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
@@ -51,13 +55,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
     assert (b.shape[1] if b_mn else b.shape[0]) == N, (b.shape, out.shape, b_mn)
     assert (b.shape[0] if b_mn else b.shape[1]) == K
     out_fp32 = out.dtype == torch.float32
+    if colsum is not None:
+        assert colsum.dtype == torch.float32 and colsum.numel() == N and colsum.is_contiguous()
     aux = aux_out if aux_out is not None else aux_in
     rc = _fn()(
         _lib.ptr(a), int(a_mn), a.stride(0), _lib.ptr(b), int(b_mn), b.stride(0),
         _lib.ptr(out), out.stride(0), int(out_fp32), M, N, K, epi, split_k,
         _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
         _lib.ptr(aux_out), _lib.ptr(aux_in), aux.stride(0) if aux is not None else 0,
-        _lib.ptr(_lib.status_word(out.device)), max_ctas, _lib.stream_ptr())
+        _lib.ptr(_lib.status_word(out.device)), max_ctas, _lib.ptr(colsum), _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"z2h_gemm_bf16 failed with code {rc} for M={M} N={N} K={K}")
     return out
