@@ -21,4 +21,11 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
                       float* dq_accum, float* stats, int B, int T, int H, float drop_p,
                       const unsigned long long* seed_ptr, unsigned int site, int* status,
                       cudaStream_t stream);
+// The same again (drop_p may be 0, seed_ptr then unused) with a by-product: dbias, fp32 [3*H*64] or
+// null, receives += the column sums of dqkv as stored, which is the gradient of the bias of the
+// projection that produced qkv (nn/gpt2/modules.py:19 of the reference: c_attn has a bias).
+int flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                    float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                    const unsigned long long* seed_ptr, unsigned int site, float* dbias, int* status,
+                    cudaStream_t stream);
 }  // namespace z2h

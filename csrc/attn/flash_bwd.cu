@@ -32,6 +32,7 @@
 #include "attn.h"
 #include "../common/trace.cuh"
 #include "../common/dropout.cuh"
+#include "../common/warp_colsum.cuh"
 #include <cstdlib>
 
 namespace z2h {
@@ -73,6 +74,10 @@ struct BwdParams {
   int B, T, H, C;
   float scale, scale_log2;
   int* status;
+  // fp32 [3C] or null: the column sums of dqkv (as stored) are added here, i.e. the gradient of the
+  // QKV projection's bias; the dK / dV thirds by this kernel's epilogue, the dQ third by the
+  // conversion kernel
+  float* dbias;
   // attention-probability dropout (DROP instantiation only), same stream as the forward kernel
   float drop_p;
   const unsigned long long* seed_ptr;
@@ -461,6 +466,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       if (ok) tc_fence_after();
     }
     const int tk = j * TS + r;
+    ok = __all_sync(0xffffffffu, ok);  // the column sums below shuffle across the whole warp
     if (ok) {
       __nv_bfloat16* dk_row = p.dqkv + (long long)(row0 + tk) * (3 * p.C) + p.C + h * HD + part * 16;
       __nv_bfloat16* dv_row = dk_row + p.C;
@@ -478,6 +484,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           *reinterpret_cast<uint4*>(dv_row + q * 8) = u;
         }
       }
+      auto add_column_sums = [&](float* dst) {  // of v as rounded to bf16, rows past T left out
+        float f[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          f[e] = tk < p.T ? __bfloat162float(__float2bfloat16(__uint_as_float(v[e]))) : 0.f;
+        const float sum = warp_column_sums<16>(f, lane);  // column lane / 2, in both lanes of the pair
+        if ((lane & 1) == 0) atomicAdd(dst + h * HD + part * 16 + (lane >> 1), sum);
+      };
+      if (p.dbias != nullptr) add_column_sums(p.dbias + 2 * p.C);
       tmem_ld_32x32b_x16(t_lane + DK_COL + part * 16, v);
       tmem_ld_wait();
       if (tk < p.T) {
@@ -490,6 +505,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           u.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]) * p.scale, __uint_as_float(v[q * 8 + 7]) * p.scale);
           *reinterpret_cast<uint4*>(dk_row + q * 8) = u;
         }
+      }
+      if (p.dbias != nullptr) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * p.scale);
+        add_column_sums(p.dbias + p.C);
       }
     }
   }
@@ -563,9 +583,11 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
 // dqkv[m, 0:C] = bf16(dQ[m, :] * scale), dQ read from its blocked layout
 // [row / 32][head][16-byte column group][row % 32]: a thread converts 16 columns of one row (four
 // coalesced 16-byte loads across the warp, one 32-byte store).
+// dbias (fp32 [C] or null): the column sums of what is stored are added to it; a warp holds 32 rows
+// of the same 16 columns.
 __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
                                             __nv_bfloat16* __restrict__ dqkv, long long M, int H,
-                                            float scale) {
+                                            float scale, float* __restrict__ dbias) {
   pdl_launch_dependents();
   pdl_wait();
   const int C = H * HD;
@@ -578,18 +600,30 @@ __global__ void flash_bwd_dq_convert_kernel(const float* __restrict__ dq_accum,
     const long long bh = idx >> 7;  // == blk * H + h
     const int h = (int)(bh % H);
     const long long g = (bh / H) * 32 + lane;
-    if (g >= M) continue;
+    const bool valid = g < M;  // whole warps stay for the shuffles
     const float4* src = reinterpret_cast<const float4*>(dq_accum) + (bh * 16 + c16 * 4) * 32 + lane;
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const float4 a = src[k * 32];
+      const float4 a = valid ? src[k * 32] : make_float4(0.f, 0.f, 0.f, 0.f);
       w[2 * k] = pack_bf16x2(a.x * scale, a.y * scale);
       w[2 * k + 1] = pack_bf16x2(a.z * scale, a.w * scale);
     }
-    uint4* dst = reinterpret_cast<uint4*>(dqkv + g * 3 * C + h * HD + c16 * 16);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    if (valid) {
+      uint4* dst = reinterpret_cast<uint4*>(dqkv + g * 3 * C + h * HD + c16 * 16);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    if (dbias != nullptr) {
+      float f[16];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float2 x = unpack_bf16x2(w[k]);
+        f[2 * k] = x.x; f[2 * k + 1] = x.y;
+      }
+      const float sum = warp_column_sums<16>(f, lane);
+      if ((lane & 1) == 0) atomicAdd(dbias + h * HD + c16 * 16 + (lane >> 1), sum);
+    }
   }
 }
 
@@ -599,6 +633,14 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
                       float* dq_accum, float* stats, int B, int T, int H, float drop_p,
                       const unsigned long long* seed_ptr, unsigned int site, int* status,
                       cudaStream_t stream) {
+  return flash_bwd_dbias(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site, nullptr,
+                         status, stream);
+}
+
+int flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                    float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                    const unsigned long long* seed_ptr, unsigned int site, float* dbias, int* status,
+                    cudaStream_t stream) {
   const int C = H * HD;
   if (!(drop_p >= 0.f) || drop_p >= 1.f) return 1;
   if (B <= 0 || T <= 0) return 0;
@@ -624,6 +666,7 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
   p.scale = 0.125f;
   p.scale_log2 = 0.125f * 1.4426950408889634f;
   p.status = status;
+  p.dbias = dbias;
   p.drop_p = drop_p;
   p.seed_ptr = seed_ptr;
   p.site = site;
@@ -639,7 +682,7 @@ int flash_bwd_dropout(const void* qkv, const void* out, const void* dout, const 
     const long long total = (((long long)B * T + 31) / 32) * H * 4 * 32;
     const int grid = (int)((total + 255) / 256);
     launch_kernel(flash_bwd_dq_convert_kernel, dim3(grid), dim3(256), 0, stream, true, (const float*)dq_accum,
-                  (__nv_bfloat16*)dqkv, (long long)B * T, H, 0.125f);
+                  (__nv_bfloat16*)dqkv, (long long)B * T, H, 0.125f, dbias);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
@@ -658,6 +701,13 @@ extern "C" int z2h_flash_bwd_dropout(const void* qkv, const void* out, const voi
                                      int* status, void* stream) {
   return z2h::flash_bwd_dropout(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site,
                                 status, (cudaStream_t)stream);
+}
+extern "C" int z2h_flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const float* lse,
+                                   void* dqkv, float* dq_accum, float* stats, int B, int T, int H,
+                                   float drop_p, const unsigned long long* seed_ptr, unsigned int site,
+                                   float* dbias, int* status, void* stream) {
+  return z2h::flash_bwd_dbias(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site,
+                              dbias, status, (cudaStream_t)stream);
 }
 extern "C" long long z2h_flash_bwd_dq_elems(int B, int T, int H) {
   return (((long long)B * T + 31) / 32 * 32) * H * 64;

@@ -2,6 +2,7 @@
 #pragma once
 #include "../common/checked.cuh"
 #include "../common/ptx.cuh"
+#include "../common/warp_colsum.cuh"
 #include "gemm.h"
 #include <cstdlib>
 
@@ -164,24 +165,6 @@ __device__ __forceinline__ void st_row(void* ptr, const uint32_t (&w)[N_WORDS], 
   }
 }
 
-// Column sums of a 32 x 32 block held one row per lane (v[j] = column j of this lane's row): a
-// butterfly in which every step halves the columns a lane keeps and doubles the rows they cover.
-// After the five steps lane l holds, in v[0], the sum of column l over the warp's 32 rows:
-// 31 shuffles per block instead of 32 x 5.
-__device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
-#pragma unroll
-  for (int s = 16; s >= 1; s >>= 1) {
-    const bool upper = (lane & s) != 0;
-#pragma unroll
-    for (int j = 0; j < s; ++j) {
-      const float send = upper ? v[j] : v[j + s];
-      const float keep = upper ? v[j + s] : v[j];
-      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
-    }
-  }
-  return v[0];
-}
-
 // Epilogue of 32 consecutive columns of one output row, all of which exist; one instantiation
 // per epilogue kind and output type keeps each kernel's hot path short.
 //   r: the accumulator values (fp32 bit patterns); sbias: bias of these columns in shared memory.
@@ -263,7 +246,7 @@ __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32
         const float2 f = unpack_bf16x2(w[j]);
         v[2 * j] = f.x; v[2 * j + 1] = f.y;
       }
-      const float sum = warp_column_sums(v, (int)(threadIdx.x & 31));
+      const float sum = warp_column_sums<32>(v, (int)(threadIdx.x & 31));
       asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.colsum + gcol + (threadIdx.x & 31)), "f"(sum) : "memory");
     }
   }

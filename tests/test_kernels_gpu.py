@@ -264,6 +264,15 @@ def test_flash_attention_fwd_bwd(dev, B, T, H):
     status_ok()
     for i, name in enumerate("qkv"):
         assert rel_err(dqkv[:, i * C:(i + 1) * C], refd[:, i * C:(i + 1) * C]) < 2e-2, name
+    # the by-product: column sums of dqkv (the QKV bias gradient) added to an fp32 vector
+    start = torch.randn(3 * C, device=dev)
+    dbias = start.clone()
+    dqkv2 = torch.zeros_like(qkv)
+    N.flash_bwd(qkv, out, dout, lse, dqkv2, dqa, stats, B, T, H, dbias=dbias)
+    status_ok()
+    assert rel_err(dqkv2, dqkv) < 1e-3  # same kernels (atomic dQ accumulation: not bitwise)
+    want = start + dqkv2.float().sum(0)
+    assert (dbias - want).abs().max().item() <= 1e-4 * dqkv2.float().abs().sum(0).max().item() + 1e-4
 
 
 def test_flash_forward_run_twice_bitwise(dev):

@@ -506,12 +506,12 @@ class GPT2TrainEngine:
 
             self._on_side(wg_attn_proj)
             G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
+            # the c_attn bias gradient (column sums of d_qkv) comes out of the attention kernels
             N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
-                        self.attn_stats, B, T, H, pd, seed, 1 + 3 * l)
+                        self.attn_stats, B, T, H, pd, seed, 1 + 3 * l, dbias=gw(p + "attn.c_attn.bias"))
 
             def wg_attn_qkv(l=l, p=p):
                 self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
-                N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"))
 
             self._on_side(wg_attn_qkv)
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)

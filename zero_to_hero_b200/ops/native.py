@@ -35,6 +35,8 @@ _sigs = {
     "z2h_flash_bwd": [c_void_p] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p],
     "z2h_flash_fwd_dropout": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
                               ctypes.c_uint, c_void_p, c_void_p],
+    "z2h_flash_bwd_dbias": [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_void_p, ctypes.c_uint,
+                            c_void_p, c_void_p, c_void_p],
     "z2h_flash_bwd_dropout": [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_void_p, ctypes.c_uint,
                                                c_void_p, c_void_p],
     "z2h_dropout_apply": [c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_void_p, ctypes.c_uint,
@@ -163,9 +165,21 @@ def flash_bwd_dq_elems(B: int, T: int, H: int) -> int:
 
 
 def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p: float = 0.0, seed=None,
-              site: int = 0):
+              site: int = 0, dbias=None):
+    """`dbias` (fp32 [3*H*64]): the column sums of `dqkv` as stored are ADDED to it, i.e. the gradient
+    of the QKV projection's bias comes out of the attention backward kernels."""
     assert stats.numel() >= flash_bwd_stats_elems(B, T, H)
     assert dq_accum.numel() >= flash_bwd_dq_elems(B, T, H) and dq_accum.dtype == torch.float32
+    if dbias is not None:
+        assert dbias.dtype == torch.float32 and dbias.numel() == 3 * H * 64 and dbias.is_contiguous()
+        if drop_p > 0.0:
+            assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
+        _check(_f("z2h_flash_bwd_dbias")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
+                                         ptr(dq_accum), ptr(stats), B, T, H, drop_p,
+                                         ptr(seed) if drop_p > 0.0 else None, site, ptr(dbias),
+                                         ptr(_lib.status_word(out.device)), stream_ptr()),
+               "flash_bwd_dbias")
+        return
     if drop_p > 0.0:
         assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
         _check(_f("z2h_flash_bwd_dropout")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv),
