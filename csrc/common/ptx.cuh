@@ -360,6 +360,30 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
+// tanh-GELU and its derivative for a pair of values with packed arithmetic: 5 and 11 packed
+// instructions plus two tanh.approx per pair (the scalar forms above cost about 9 and 17 per
+// value). Same formulas, constants folded:
+//   u = x (k0 + k0 k1 x^2);  gelu = h + h tanh(u) with h = x / 2
+//   gelu' = (1/2 + t/2) + a - a t^2 with t = tanh(u), a = x (k0/2 + 3 k0 k1 / 2 x^2)
+__device__ __forceinline__ float2 gelu_tanh2(float2 x) {
+  const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+  const float2 x2 = mul2(x, x);
+  const float2 u = mul2(x, fma2(x2, make_float2(k01, k01), make_float2(k0, k0)));
+  const float2 t = make_float2(tanh_fast(u.x), tanh_fast(u.y));
+  const float2 h = mul2(x, make_float2(0.5f, 0.5f));
+  return fma2(h, t, h);
+}
+__device__ __forceinline__ float2 gelu_tanh_grad2(float2 x) {
+  const float k0 = 0.7978845608028654f, k01 = 0.7978845608028654f * 0.044715f;
+  const float2 x2 = mul2(x, x);
+  const float2 u = mul2(x, fma2(x2, make_float2(k01, k01), make_float2(k0, k0)));
+  const float2 t = make_float2(tanh_fast(u.x), tanh_fast(u.y));
+  const float2 a = mul2(x, fma2(x2, make_float2(1.5f * k01, 1.5f * k01), make_float2(0.5f * k0, 0.5f * k0)));
+  const float2 b = fma2(t, make_float2(0.5f, 0.5f), make_float2(0.5f, 0.5f));
+  const float2 c = mul2(a, mul2(t, t));
+  return fma2(c, make_float2(-1.f, -1.f), add2(a, b));
+}
+
 // 2^x for a pair of values on the FMA and integer pipes, no special-function unit: round x to
 // the nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on
 // [-0.5, 0.5] (relative error 7.5e-5, far below bf16 rounding) and add n to the exponent field.
@@ -467,6 +491,16 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
 // Arrive (release, cluster scope) on the barrier at this offset in the leader CTA.
 __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) &
+                                                                                   kPeerBitMask)
+               : "memory");
+}
+// The same without release semantics, for a hand-over that publishes no memory: the epilogue warps
+// tell the MMA thread that an accumulator has been read out of tensor memory (the reads have
+// completed, tcgen05.wait::ld, and are ordered by tcgen05.fence::before_thread_sync). A release at
+// cluster scope would also wait for the warp's global stores of the previous tile to be performed,
+// which showed as membar stalls (0.4 per issued instruction) in the GELU-gradient GEMM.
+__device__ __forceinline__ void mbar_arrive_leader_relaxed(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) &
                                                                                    kPeerBitMask)
                : "memory");
 }

@@ -168,56 +168,48 @@ __device__ __forceinline__ void st_row(void* ptr, const uint32_t (&w)[N_WORDS], 
 // Epilogue of 32 consecutive columns of one output row, all of which exist; one instantiation
 // per epilogue kind and output type keeps each kernel's hot path short.
 //   r: the accumulator values (fp32 bit patterns); sbias: bias of these columns in shared memory.
+//   pre: for kEpiResidual / kEpiGeluGrad, the 32 bf16 values of the second operand (residual or
+//        pre-activation) of these columns, loaded by the caller ahead of time; unused otherwise.
 template <int EPI, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32_t (&r)[32], long long grow,
-                                             int gcol, const float* sbias) {
+                                             int gcol, const float* sbias, const uint32_t (&pre)[16]) {
   if (!in_bounds_2d(grow, 1, p.M, gcol, 32, p.N, p.status, kSiteGemmRow)) return;
   const bool wide = p.wide != 0;
-  float v[32];
+  // two columns per step with packed fp32 arithmetic: the epilogue warps (two per scheduler) are
+  // bound by the instructions they issue, and the packed forms halve those
+  float2 v[16];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  for (int j = 0; j < 16; ++j) v[j] = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
   if (sbias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const float4 b = *reinterpret_cast<const float4*>(sbias + j);  // same address in all lanes
-      v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+    for (int j = 0; j < 16; j += 2) {
+      const float4 b = *reinterpret_cast<const float4*>(sbias + 2 * j);  // same address in all lanes
+      v[j] = add2(v[j], make_float2(b.x, b.y));
+      v[j + 1] = add2(v[j + 1], make_float2(b.z, b.w));
     }
   }
   if (EPI == kEpiResidual) {
-    uint32_t w[16];
-    ld_row(p.residual + grow * p.ldr + gcol, w, wide);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float2 f = unpack_bf16x2(w[j]);
-      v[2 * j] += f.x; v[2 * j + 1] += f.y;
-    }
+    for (int j = 0; j < 16; ++j) v[j] = add2(v[j], unpack_bf16x2(pre[j]));
   } else if (EPI == kEpiGelu) {
     // keep the pre-activation for the backward pass, output the activation of its bf16 rounding
     uint32_t w[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[j].x, v[j].y);
     st_row(p.aux_out + grow * p.ldaux + gcol, w, wide);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float2 f = unpack_bf16x2(w[j]);
-      v[2 * j] = gelu_tanh(f.x); v[2 * j + 1] = gelu_tanh(f.y);
-    }
+    for (int j = 0; j < 16; ++j) v[j] = gelu_tanh2(unpack_bf16x2(w[j]));
   } else if (EPI == kEpiGeluGrad) {
-    uint32_t w[16];
-    ld_row(p.aux_in + grow * p.ldaux + gcol, w, wide);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float2 f = unpack_bf16x2(w[j]);
-      v[2 * j] *= gelu_tanh_grad(f.x); v[2 * j + 1] *= gelu_tanh_grad(f.y);
-    }
+    for (int j = 0; j < 16; ++j) v[j] = mul2(v[j], gelu_tanh_grad2(unpack_bf16x2(pre[j])));
   }
   if (OUT_FP32) {
     float* cp = reinterpret_cast<float*>(p.C) + grow * p.ldc + gcol;
     if (EPI == kEpiAtomicAdd) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4), "f"(v[q * 4 + 0]),
-                     "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4), "f"(v[2 * q].x),
+                     "f"(v[2 * q].y), "f"(v[2 * q + 1].x), "f"(v[2 * q + 1].y)
                      : "memory");
       }
     } else {
@@ -225,28 +217,36 @@ __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32
       if (EPI == kEpiAccumulate) {
         ld_row(cp, w, wide);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) + v[j]);
+        for (int j = 0; j < 16; ++j) {
+          const float2 s2 = add2(v[j], make_float2(__uint_as_float(w[2 * j]), __uint_as_float(w[2 * j + 1])));
+          w[2 * j] = __float_as_uint(s2.x);
+          w[2 * j + 1] = __float_as_uint(s2.y);
+        }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
+        for (int j = 0; j < 16; ++j) {
+          w[2 * j] = __float_as_uint(v[j].x);
+          w[2 * j + 1] = __float_as_uint(v[j].y);
+        }
       }
       st_row(cp, w, wide);
     }
   } else {
     uint32_t w[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    for (int j = 0; j < 16; ++j) w[j] = pack_bf16x2(v[j].x, v[j].y);
     st_row(reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + gcol, w, wide);
     if (p.colsum != nullptr) {
       // bias gradient of the layer whose output gradient this GEMM produces: sum what was stored
       // (the rounded values, as a separate pass over C would). The launcher admits this only when
       // M is a multiple of 32, so all 32 lanes of the warp are here.
+      float t[32];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 f = unpack_bf16x2(w[j]);
-        v[2 * j] = f.x; v[2 * j + 1] = f.y;
+        t[2 * j] = f.x; t[2 * j + 1] = f.y;
       }
-      const float sum = warp_column_sums<32>(v, (int)(threadIdx.x & 31));
+      const float sum = warp_column_sums<32>(t, (int)(threadIdx.x & 31));
       asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.colsum + gcol + (threadIdx.x & 31)), "f"(sum) : "memory");
     }
   }
@@ -295,14 +295,28 @@ static __device__ __noinline__ void epilogue_row_edge(int epi, int out_fp32, voi
 // Epilogue of the four 32-column blocks a warp owns in one tile: r[c] holds block c of the row
 // `grow` (one row per lane), gcol0 is the first column of block 0, sbias the warp's staged bias
 // (128 floats, zero past N) or null.
+//
+// The residual / pre-activation operand of block c + 1 is loaded before block c is worked on. One
+// row per lane means every such load is a long-latency access of its own (32 rows, 32 sectors), the
+// eight epilogue warps of a CTA cannot hide it, and with short main loops (K = 768) the epilogue,
+// not the tensor pipe, then sets the tile time: the GELU-gradient GEMM of the MLP ran at 128 us
+// against 66 us for the same product with a plain epilogue.
 template <int EPI, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uint32_t (&r)[4][32],
                                                 long long grow, int gcol0, const float* sbias) {
+  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad;
+  const __nv_bfloat16* src = nullptr;
+  if (EPI == kEpiResidual) src = p.residual + grow * p.ldr;
+  if (EPI == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux;
+  const bool wide = p.wide != 0;
+  uint32_t pre[2][16] = {};
+  if (kSecondOperand && gcol0 + 32 <= p.N) ld_row(src + gcol0, pre[0], wide);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int gcol = gcol0 + c * 32;
+    if (kSecondOperand && c + 1 < 4 && gcol + 64 <= p.N) ld_row(src + gcol + 32, pre[(c + 1) & 1], wide);
     if (gcol + 32 <= p.N) {
-      epilogue_row<EPI, OUT_FP32>(p, r[c], grow, gcol, sbias != nullptr ? sbias + c * 32 : nullptr);
+      epilogue_row<EPI, OUT_FP32>(p, r[c], grow, gcol, sbias != nullptr ? sbias + c * 32 : nullptr, pre[c & 1]);
     } else if (gcol < p.N) {
       uint32_t tmp[32];  // addressable copy for the rolled loop
 #pragma unroll
@@ -393,6 +407,133 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const uint3
                         );
     }
   }
+}
+
+// ---- the tile epilogue, streamed over the warp's four 32-column blocks --------------------------
+// Waits for the outstanding tensor-memory load and tells the compiler that r is written HERE (the
+// load itself is asynchronous: a copy of r made between the load and this wait would hold garbage).
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+constexpr int kEpiGeneric = -1;  // any kind / output type without an instantiation: element by element
+
+// One 32 x 32 block: r = accumulator row of this lane, pre = its second operand (if the kind has one).
+template <int EPI, bool OUT_FP32>
+__device__ __forceinline__ void epilogue_block(const KernelParams& p, const uint32_t (&r)[32],
+                                               const uint32_t (&pre)[16], long long grow, int gcol,
+                                               const float* sbias, int lane, uint32_t stage, bool row_ok,
+                                               bool atomic_interior) {
+  if (OUT_FP32 && EPI == kEpiAtomicAdd) {
+    if (atomic_interior) {  // the same for the whole warp
+      epilogue_block_atomic(p, r, grow - lane, gcol, lane, stage);
+      return;
+    }
+  }
+  if (!row_ok || gcol >= p.N) return;
+  if (EPI != kEpiGeneric && gcol + 32 <= p.N) {
+    epilogue_row<EPI == kEpiGeneric ? kEpiNone : EPI, OUT_FP32>(p, r, grow, gcol, sbias, pre);
+  } else {
+    uint32_t tmp[32];  // addressable copy for the rolled loop
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tmp[j] = r[j];
+    epilogue_row_edge(p.epi, p.out_fp32, p.C, p.ldc, p.residual, p.ldr, p.aux_out, p.aux_in, p.ldaux, tmp,
+                      grow, gcol, min(32, p.N - gcol), sbias
+#ifdef Z2H_BOUNDS
+                      , p.M, p.N, p.status
+#endif
+                      );
+  }
+}
+
+// The warp's four blocks, two register buffers: while block c is worked on, the tensor-memory load
+// of block c + 1 and the load of its second operand (residual or pre-activation) are in flight. A
+// tensor-memory load issued while MMAs are queued takes around a thousand cycles and one row per
+// lane makes every global load a long-latency access of its own; with all four blocks loaded up
+// front (128 registers) nothing was left to overlap either with, and the GELU-gradient GEMM of the
+// MLP (K = 768, a short main loop) took 128 us against 66 us with a plain epilogue. The accumulator
+// is handed back (release()) when its last block is in registers.
+//   taddr: tensor-memory address of the warp's first block; active: false for a tile that has no
+//   k-blocks in this worker's share (the accumulator protocol still runs).
+template <int EPI, bool OUT_FP32, class Release>
+__device__ __forceinline__ void epilogue_stream(const KernelParams& p, uint32_t taddr, long long grow,
+                                                int gcol0, const float* sbias, int lane, uint32_t stage,
+                                                bool active, Release release) {
+  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad;
+  const bool row_ok = active && grow < p.M;
+  const bool atomic_interior = OUT_FP32 && EPI == kEpiAtomicAdd && active && sbias == nullptr &&
+                               (grow - lane) + 32 <= p.M && gcol0 + 128 <= p.N;
+  const __nv_bfloat16* src = nullptr;
+  if (EPI == kEpiResidual) src = p.residual + grow * p.ldr + gcol0;
+  if (EPI == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux + gcol0;
+  const bool wide = p.wide != 0;
+  uint32_t r[2][32];
+  uint32_t pre[2][16] = {};
+  tmem_ld_32x32b_x32(taddr, r[0]);
+  if (kSecondOperand && row_ok && gcol0 + 32 <= p.N) ld_row(src, pre[0], wide);
+#pragma unroll 1
+  for (int c = 0; c < 4; c += 2) {
+    tmem_ld_wait_for(r[0]);
+    tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[1]);
+    if (kSecondOperand && row_ok && gcol0 + (c + 2) * 32 <= p.N) ld_row(src + (c + 1) * 32, pre[1], wide);
+    epilogue_block<EPI, OUT_FP32>(p, r[0], pre[0], grow, gcol0 + c * 32,
+                                  sbias != nullptr ? sbias + c * 32 : nullptr, lane, stage, row_ok, atomic_interior);
+    tmem_ld_wait_for(r[1]);
+    if (c + 2 < 4) {
+      tmem_ld_32x32b_x32(taddr + (c + 2) * 32, r[0]);
+      if (kSecondOperand && row_ok && gcol0 + (c + 3) * 32 <= p.N) ld_row(src + (c + 2) * 32, pre[0], wide);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) release();
+    }
+    epilogue_block<EPI, OUT_FP32>(p, r[1], pre[1], grow, gcol0 + (c + 1) * 32,
+                                  sbias != nullptr ? sbias + (c + 1) * 32 : nullptr, lane, stage, row_ok,
+                                  atomic_interior);
+  }
+}
+
+//   stage: shared address of the warp's 4 KiB buffer (used by the atomic epilogue only)
+template <class Release>
+__device__ __forceinline__ void epilogue_tile_streamed(const KernelParams& p, uint32_t taddr, long long grow,
+                                                       int gcol0, const float* sbias, int lane, uint32_t stage,
+                                                       bool active, Release release) {
+  if (p.out_fp32) {
+    if (p.epi == kEpiAtomicAdd)
+      return epilogue_stream<kEpiAtomicAdd, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiAccumulate)
+      return epilogue_stream<kEpiAccumulate, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiNone)
+      return epilogue_stream<kEpiNone, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+  } else {
+    if (p.epi == kEpiNone)
+      return epilogue_stream<kEpiNone, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiResidual)
+      return epilogue_stream<kEpiResidual, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiGelu)
+      return epilogue_stream<kEpiGelu, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiGeluGrad)
+      return epilogue_stream<kEpiGeluGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+  }
+  return epilogue_stream<kEpiGeneric, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+}
+
+// Called before the wait for the accumulator: asks L2 for this lane's 128 columns (256 bytes) of the
+// epilogue's second operand, so that the loads after the wait find them there instead of in DRAM.
+__device__ __forceinline__ void prefetch_second_operand(const KernelParams& p, long long grow, int gcol0) {
+  const __nv_bfloat16* src = nullptr;
+  if (p.epi == kEpiResidual) src = p.residual + grow * p.ldr + gcol0;
+  else if (p.epi == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux + gcol0;
+  if (src == nullptr || grow >= p.M) return;
+  if (gcol0 < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+  if (gcol0 + 64 < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));
 }
 
 // Each epilogue warp copies the bias of the 128 columns it will drain into its own slice of

@@ -213,6 +213,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       // bias of this warp's 128 columns, staged before the wait for the accumulator
       const int gcol0 = nt * BN + half * 128;
       const float* sbias = gemm_detail::stage_bias(p, epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats, gcol0, lane);
+      if (!empty_split) gemm_detail::prefetch_second_operand(p, (long long)mt * BM + quarter * 32 + lane, gcol0);
       if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
@@ -223,21 +224,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       // this warp drains 4 of the 8 column blocks of its 32 rows
       const int c0 = half * 4;
-      // All four TMEM loads are issued back to back and awaited once: a load issued while the
-      // tensor core has MMAs queued completes only after ~1000 cycles, and paying that once
-      // per tile instead of once per block is what keeps the epilogue shorter than the main
-      // loop. The accumulator is handed back as soon as it is in registers.
-      uint32_t r[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + (c0 + c) * 32, r[c]);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-      if (warp == 2 && lane == 0) Z2H_TRACE();
-      if (!empty_split)
-        gemm_detail::epilogue_tile(p, r, row_base + lane, gcol0, sbias, lane,
-                                   smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats));
+      uint64_t* const tempty = &tempty_bar[acc];
+      gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
+                                          smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
+                                          !empty_split, [tempty] { mbar_arrive(tempty); });
       if (warp == 2 && lane == 0) Z2H_TRACE();
     }
   }

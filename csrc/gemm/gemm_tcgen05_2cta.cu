@@ -44,7 +44,10 @@ constexpr int SMEM_BYTES =
     STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_WARPS * gemm_detail::kEpiWarpBytes;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 
-template <int A_MN, int B_MN>
+// FIXUP: the instantiation that can run stream-K with fix-up (KernelParams::stream_k == 2). Its
+// epilogue needs a warp's whole piece of a tile in registers at once, which costs register spills;
+// the kernels every other launch uses are compiled without that path.
+template <int A_MN, int B_MN, bool FIXUP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const KernelParams p) {
@@ -210,6 +213,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       // bias of this warp's 128 columns, staged before the wait for the accumulator
       const int gcol0 = nt * BN + half * 128;
       const float* sbias = gemm_detail::stage_bias(p, epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats, gcol0, lane);
+      if (!empty_split) gemm_detail::prefetch_second_operand(p, (long long)mt * TM + (long long)rank * HM + quarter * 32 + lane, gcol0);
       if (!mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
@@ -220,10 +224,17 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       // this warp drains 4 of the 8 column blocks of its 32 rows
       const int c0 = half * 4;
-      // All four TMEM loads are issued back to back and awaited once: a load issued while the
-      // tensor core has MMAs queued completes only after ~1000 cycles, and paying that once
-      // per tile instead of once per block is what keeps the epilogue shorter than the main
-      // loop. The accumulator is handed back as soon as it is in registers.
+      uint64_t* const tempty = &tempty_bar[acc];
+      if (!FIXUP || p.stream_k != 2) {
+        gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
+                                            smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
+                                            !empty_split, [tempty] { mbar_arrive_leader_relaxed(tempty); });
+        if (warp == 2 && lane == 0) Z2H_TRACE();
+        continue;
+      }
+      // Stream-K with fix-up needs the warp's whole 32 x 128 piece at once (it is parked in, or
+      // completed from, the workspace): all four tensor-memory loads issued back to back and
+      // awaited once, the accumulator handed back as soon as it is in registers.
       uint32_t r[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + (c0 + c) * 32, r[c]);
@@ -390,10 +401,12 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
     }
   }
 
-  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  auto kern = p.stream_k == 2 ? gemm_bf16_2cta_kernel<A_MN, B_MN, true> : gemm_bf16_2cta_kernel<A_MN, B_MN, false>;
   static std::atomic<unsigned long long> attr_seen{0};
-  if (first_use_on_current_device(attr_seen))
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (first_use_on_current_device(attr_seen)) {
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  }
   const int num_sms = num_sms_all;
   const long long tiles = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) *
                           (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);

@@ -107,6 +107,14 @@ def build_all(force: bool = False, verbose: bool = False, bounds: bool = False) 
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {r.stderr}")
     out["host"] = host_lib
+    # objects of earlier header states are never used again: drop them, keeping both flavours of the
+    # current state (the cache otherwise grows by a full set per header edit)
+    keep = {stamp.rstrip("b"), stamp.rstrip("b") + "b"}
+    if OBJDIR.exists():
+        for old in OBJDIR.rglob("*.o"):
+            parts = old.name.split(".")
+            if len(parts) >= 3 and parts[-2] not in keep:
+                old.unlink(missing_ok=True)
     return out
 
 
