@@ -540,3 +540,15 @@ def test_flash_attention_dropout_against_masked_reference(dev, B, T, H):
     assert rel_err(out, ref) < 2e-2
     assert rel_err(dqkv, x.grad.reshape(B * T, 3 * C)) < 3e-2
     status_ok()
+
+
+def test_mma_probe_reports_sane_costs(dev):
+    """The tcgen05.mma cost probe runs to completion (its wait is bounded) and its figures keep the
+    order the attention kernels are designed around: wider outputs cost more, an A operand in tensor
+    memory costs less than one in shared memory."""
+    from zero_to_hero_b200.utils.mma_probe import probe
+    n64 = probe(0, 64, 0)["done_cycles_per_mma"]
+    n256 = probe(2, 64, 0)["done_cycles_per_mma"]
+    ts64 = probe(5, 64, 0)["done_cycles_per_mma"]
+    assert 20 < ts64 < n64 < n256 < 400, (ts64, n64, n256)
+    status_ok()

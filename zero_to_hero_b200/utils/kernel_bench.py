@@ -81,8 +81,19 @@ def bench_gemm(a, dev):
     kw = {}
     if a.split_k > 1 or a.split_k == 0:  # 0: stream-K schedule
         kw = dict(epi=G.EPI_ATOMIC_ADD, split_k=a.split_k)
+    tag = ""
+    if a.epi != "none":  # the fused epilogues of the MLP and the projections (bf16 output)
+        other = torch.randn(M, Nn, device=dev).bfloat16()
+        bias = torch.randn(Nn, device=dev).bfloat16()
+        kw = {"bias": dict(bias=bias),
+              "gelu": dict(bias=bias, aux_out=other, epi=G.EPI_GELU),
+              "gelu_grad": dict(aux_in=other, epi=G.EPI_GELU_GRAD),
+              "residual": dict(bias=bias, residual=other, epi=G.EPI_RESIDUAL)}[a.epi]
+        if a.colsum:
+            kw["colsum"] = torch.zeros(Nn, device=dev)
+        tag = f" epi={a.epi}{'+colsum' if a.colsum else ''}"
     ms = time_kernel(lambda: G.gemm(A, B, out, a_mn=a.a_mn, b_mn=a.b_mn, **kw), a.iters, flush=not a.no_flush)
-    report(f"gemm M{M} N{Nn} K{K} a_mn{int(a.a_mn)} b_mn{int(a.b_mn)} split{a.split_k}", ms,
+    report(f"gemm M{M} N{Nn} K{K} a_mn{int(a.a_mn)} b_mn{int(a.b_mn)} split{a.split_k}{tag}", ms,
            flops=2.0 * M * Nn * K)
     if a.compare and not (a.a_mn or a.b_mn):
         ms2 = time_kernel(lambda: torch.matmul(A, B.t()), a.iters, flush=not a.no_flush)
@@ -213,6 +224,9 @@ def bench_sample(a, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
+    ap.add_argument("--epi", default="none", choices=["none", "bias", "gelu", "gelu_grad", "residual"],
+                    help="gemm: fused epilogue to time")
+    ap.add_argument("--colsum", action="store_true", help="gemm: also produce the column sums of the output")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=768)
