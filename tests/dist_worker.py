@@ -59,6 +59,9 @@ def main():
         mon.beat(0)
         mon.wait_all(0)
         if rank == world - 1:
+            # leaves between steps: only once every peer has started step 1 (a "left" written
+            # while a slow peer still waits for step 0 would replace the beat that peer needs)
+            mon.wait_all(1)
             mon.leave()
             print(f"OK rank {rank} left")
             os._exit(0)
