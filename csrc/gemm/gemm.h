@@ -12,6 +12,11 @@ enum GemmEpilogue : int {
   kEpiGeluGrad = 3,    // C = acc * gelu_tanh'(aux_in)
   kEpiAtomicAdd = 4,   // C(fp32) += acc with red.global.add (split-K capable)
   kEpiAccumulate = 5,  // C(fp32) += acc with plain read-modify-write (deterministic)
+  // The pair a training step uses for the MLP: the forward GEMM stores the DERIVATIVE of the
+  // activation instead of the pre-activation (the backward needs nothing else of it, and both share
+  // one tanh), so the backward epilogue is one load and one multiply instead of a second GELU'.
+  kEpiGeluSaveGrad = 6,  // x = acc (+ bias); aux_out = gelu_tanh'(x); C = gelu_tanh(x)
+  kEpiMulAux = 7,        // C = acc * aux_in
 };
 
 // C[M,N] = A * B^T in the logical sense: A is M x K, B is N x K.

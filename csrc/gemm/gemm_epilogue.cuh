@@ -202,6 +202,19 @@ __device__ __forceinline__ void epilogue_row(const KernelParams& p, const uint32
   } else if (EPI == kEpiGeluGrad) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = mul2(v[j], gelu_tanh_grad2(unpack_bf16x2(pre[j])));
+  } else if (EPI == kEpiGeluSaveGrad) {
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float2 act, grad;
+      gelu_tanh_with_grad2(v[j], act, grad);
+      w[j] = pack_bf16x2(grad.x, grad.y);
+      v[j] = act;
+    }
+    st_row(p.aux_out + grow * p.ldaux + gcol, w, wide);
+  } else if (EPI == kEpiMulAux) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = mul2(v[j], unpack_bf16x2(pre[j]));
   }
   if (OUT_FP32) {
     float* cp = reinterpret_cast<float*>(p.C) + grow * p.ldc + gcol;
@@ -280,6 +293,11 @@ static __device__ __noinline__ void epilogue_row_edge(int epi, int out_fp32, voi
       v = gelu_tanh(__bfloat162float(pre));
     } else if (epi == kEpiGeluGrad) {
       v *= gelu_tanh_grad(__bfloat162float(aux_in[grow * ldaux + col]));
+    } else if (epi == kEpiGeluSaveGrad) {
+      aux_out[grow * ldaux + col] = __float2bfloat16(gelu_tanh_grad(v));
+      v = gelu_tanh(v);
+    } else if (epi == kEpiMulAux) {
+      v *= __bfloat162float(aux_in[grow * ldaux + col]);
     }
     if (out_fp32) {
       float* cp = reinterpret_cast<float*>(C) + grow * ldc + col;
@@ -304,10 +322,10 @@ static __device__ __noinline__ void epilogue_row_edge(int epi, int out_fp32, voi
 template <int EPI, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_blocks(const KernelParams& p, const uint32_t (&r)[4][32],
                                                 long long grow, int gcol0, const float* sbias) {
-  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad;
+  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad || EPI == kEpiMulAux;
   const __nv_bfloat16* src = nullptr;
   if (EPI == kEpiResidual) src = p.residual + grow * p.ldr;
-  if (EPI == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux;
+  if (EPI == kEpiGeluGrad || EPI == kEpiMulAux) src = p.aux_in + grow * p.ldaux;
   const bool wide = p.wide != 0;
   uint32_t pre[2][16] = {};
   if (kSecondOperand && gcol0 + 32 <= p.N) ld_row(src + gcol0, pre[0], wide);
@@ -466,13 +484,13 @@ template <int EPI, bool OUT_FP32, class Release>
 __device__ __forceinline__ void epilogue_stream(const KernelParams& p, uint32_t taddr, long long grow,
                                                 int gcol0, const float* sbias, int lane, uint32_t stage,
                                                 bool active, Release release) {
-  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad;
+  constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad || EPI == kEpiMulAux;
   const bool row_ok = active && grow < p.M;
   const bool atomic_interior = OUT_FP32 && EPI == kEpiAtomicAdd && active && sbias == nullptr &&
                                (grow - lane) + 32 <= p.M && gcol0 + 128 <= p.N;
   const __nv_bfloat16* src = nullptr;
   if (EPI == kEpiResidual) src = p.residual + grow * p.ldr + gcol0;
-  if (EPI == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux + gcol0;
+  if (EPI == kEpiGeluGrad || EPI == kEpiMulAux) src = p.aux_in + grow * p.ldaux + gcol0;
   const bool wide = p.wide != 0;
   uint32_t r[2][32];
   uint32_t pre[2][16] = {};
@@ -521,6 +539,10 @@ __device__ __forceinline__ void epilogue_tile_streamed(const KernelParams& p, ui
       return epilogue_stream<kEpiGelu, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
     if (p.epi == kEpiGeluGrad)
       return epilogue_stream<kEpiGeluGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiGeluSaveGrad)
+      return epilogue_stream<kEpiGeluSaveGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+    if (p.epi == kEpiMulAux)
+      return epilogue_stream<kEpiMulAux, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
   }
   return epilogue_stream<kEpiGeneric, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
 }
@@ -530,7 +552,7 @@ __device__ __forceinline__ void epilogue_tile_streamed(const KernelParams& p, ui
 __device__ __forceinline__ void prefetch_second_operand(const KernelParams& p, long long grow, int gcol0) {
   const __nv_bfloat16* src = nullptr;
   if (p.epi == kEpiResidual) src = p.residual + grow * p.ldr + gcol0;
-  else if (p.epi == kEpiGeluGrad) src = p.aux_in + grow * p.ldaux + gcol0;
+  else if (p.epi == kEpiGeluGrad || p.epi == kEpiMulAux) src = p.aux_in + grow * p.ldaux + gcol0;
   if (src == nullptr || grow >= p.M) return;
   if (gcol0 < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
   if (gcol0 + 64 < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 64));

@@ -291,6 +291,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   if (g.epi == kEpiResidual && (g.residual == nullptr || (g.ldr % 8))) return 1;
   if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
+  if (g.epi == kEpiGeluSaveGrad && (g.aux_out == nullptr || (g.ldaux % 8) || g.out_fp32)) return 1;
+  if (g.epi == kEpiMulAux && (g.aux_in == nullptr || (g.ldaux % 8) || g.out_fp32)) return 1;
+  if (g.epi < kEpiNone || g.epi > kEpiMulAux) return 1;
   if (reinterpret_cast<uintptr_t>(g.bias) & 7) return 1;
   if (g.colsum != nullptr && (g.out_fp32 || g.split_k != 1 || (g.M % 32) || (g.N % 32) ||
                               (reinterpret_cast<uintptr_t>(g.colsum) & 3)))

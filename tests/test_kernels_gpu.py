@@ -152,6 +152,15 @@ def test_gemm_epilogues(dev):
     F.gelu(x, approximate="tanh").sum().backward()
     G.gemm(A, B, out, aux_in=pre, epi=G.EPI_GELU_GRAD)
     assert rel_err(out, base * x.grad) < 1e-2
+    # the training pair: the forward stores gelu'(x), the backward multiplies by it
+    deriv = torch.empty_like(out)
+    G.gemm(A, B, out, bias=bias, aux_out=deriv, epi=G.EPI_GELU_SAVE_GRAD)
+    xb = (base + bias.float()).requires_grad_(True)
+    F.gelu(xb, approximate="tanh").sum().backward()
+    assert rel_err(out, F.gelu(xb.detach(), approximate="tanh")) < 1e-2
+    assert rel_err(deriv, xb.grad) < 1e-2
+    G.gemm(A, B, out, aux_in=deriv, epi=G.EPI_MUL_AUX)
+    assert rel_err(out, base * deriv.float()) < 1e-2
     o32 = torch.zeros(M, N, device=dev)
     G.gemm(A, B, o32, epi=G.EPI_ATOMIC_ADD, split_k=3)
     assert rel_err(o32, base) < 1e-4

@@ -372,8 +372,10 @@ class GPT2TrainEngine:
                 G.gemm(att, w(p + "attn.c_proj.weight"), x_mid, bias=w(p + "attn.c_proj.bias"),
                        residual=resid[l], epi=G.EPI_RESIDUAL)
             N.layernorm_fwd(x_mid, w(p + "ln_2.weight"), lnb(p + "ln_2.bias"), xn2, st[2], st[3])
+            # `pre` receives gelu'(x), not x: the backward needs nothing else of the pre-activation,
+            # and its GEMM epilogue becomes one load and one multiply
             G.gemm(xn2, w(p + "mlp.c_fc.weight"), act, bias=w(p + "mlp.c_fc.bias"), aux_out=pre,
-                   epi=G.EPI_GELU)
+                   epi=G.EPI_GELU_SAVE_GRAD)
             if pd > 0.0:
                 tmp = rows(self.drop_tmp)
                 G.gemm(act, w(p + "mlp.c_proj.weight"), tmp, bias=w(p + "mlp.c_proj.bias"))
@@ -481,7 +483,7 @@ class GPT2TrainEngine:
             # 124M step, 971-972 k tokens/s with the by-product against 973-975 k without.
             fc_db_in_gemm = self.M % 32 == 0 and os.environ.get("Z2H_FC_BIAS_IN_GEMM", "0") == "1"
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
-                   aux_in=self.pre[l], epi=G.EPI_GELU_GRAD,
+                   aux_in=self.pre[l], epi=G.EPI_MUL_AUX,
                    colsum=gw(p + "mlp.c_fc.bias") if fc_db_in_gemm else None)
 
             def wg_mlp_fc(l=l, p=p, fc_db_in_gemm=fc_db_in_gemm):

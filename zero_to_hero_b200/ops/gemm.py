@@ -7,7 +7,8 @@ import torch
 
 from . import _lib
 
-EPI_NONE, EPI_RESIDUAL, EPI_GELU, EPI_GELU_GRAD, EPI_ATOMIC_ADD, EPI_ACCUMULATE = range(6)
+(EPI_NONE, EPI_RESIDUAL, EPI_GELU, EPI_GELU_GRAD, EPI_ATOMIC_ADD, EPI_ACCUMULATE, EPI_GELU_SAVE_GRAD,
+ EPI_MUL_AUX) = range(8)
 
 _configured = False
 

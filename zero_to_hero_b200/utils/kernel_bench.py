@@ -88,6 +88,8 @@ def bench_gemm(a, dev):
         kw = {"bias": dict(bias=bias),
               "gelu": dict(bias=bias, aux_out=other, epi=G.EPI_GELU),
               "gelu_grad": dict(aux_in=other, epi=G.EPI_GELU_GRAD),
+              "gelu_save_grad": dict(bias=bias, aux_out=other, epi=G.EPI_GELU_SAVE_GRAD),
+              "mul_aux": dict(aux_in=other, epi=G.EPI_MUL_AUX),
               "residual": dict(bias=bias, residual=other, epi=G.EPI_RESIDUAL)}[a.epi]
         if a.colsum:
             kw["colsum"] = torch.zeros(Nn, device=dev)
@@ -224,7 +226,7 @@ def bench_sample(a, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
-    ap.add_argument("--epi", default="none", choices=["none", "bias", "gelu", "gelu_grad", "residual"],
+    ap.add_argument("--epi", default="none", choices=["none", "bias", "gelu", "gelu_grad", "gelu_save_grad", "mul_aux", "residual"],
                     help="gemm: fused epilogue to time")
     ap.add_argument("--colsum", action="store_true", help="gemm: also produce the column sums of the output")
     ap.add_argument("--M", type=int, default=16384)
