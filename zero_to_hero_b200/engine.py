@@ -476,12 +476,12 @@ class GPT2TrainEngine:
                     N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
 
             self._on_side(wg_mlp_proj)
-            # The c_fc bias gradient is the column sum of d_4c. The GEMM's epilogue can produce it
-            # as a by-product (Z2H_FC_BIAS_IN_GEMM=1; needs whole warps of rows), but this GEMM is
-            # bound by its epilogue (GELU gradient), where the column butterfly costs 13 us, while
-            # the separate pass runs on the side stream under tensor-bound GEMMs: measured on the
-            # 124M step, 971-972 k tokens/s with the by-product against 973-975 k without.
-            fc_db_in_gemm = self.M % 32 == 0 and os.environ.get("Z2H_FC_BIAS_IN_GEMM", "0") == "1"
+            # The c_fc bias gradient is the column sum of d_4c: a by-product of this GEMM's epilogue
+            # (a column butterfly per 32 x 32 block; needs whole warps of rows). Against the separate
+            # pass on the side stream it makes no measurable difference to the 124M step (950.3-952.6 k
+            # tokens/s with it, 950.0-957.3 k without, alternating runs on one box) and saves a launch
+            # per layer; Z2H_FC_BIAS_IN_GEMM=0 brings the separate pass back.
+            fc_db_in_gemm = self.M % 32 == 0 and os.environ.get("Z2H_FC_BIAS_IN_GEMM", "1") != "0"
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
                    aux_in=self.pre[l], epi=G.EPI_MUL_AUX,
                    colsum=gw(p + "mlp.c_fc.bias") if fc_db_in_gemm else None)
@@ -527,9 +527,10 @@ class GPT2TrainEngine:
                             self.ln_scratch,
                             dxsum=gw(f"transformer.h.{l - 1}.mlp.c_proj.bias") if fuse_db and l > 0 else None)
             cur = 1 - cur
-            # dgrad GEMMs, column sums (2 of the 4 ride in the LayerNorm backward without dropout),
-            # LN bwd (2 kernels each), flash bwd (3)
-            self._n += 4 + (2 if fuse_db else 4) + 2 * 2 + 3
+            # dgrad GEMMs, column-sum launches (the projection biases ride in the LayerNorm backward
+            # without dropout, the QKV bias in the attention kernels, the c_fc bias usually in its
+            # GEMM), LN bwd (2 kernels each), flash bwd (3)
+            self._n += 4 + (0 if fuse_db else 2) + (0 if fc_db_in_gemm else 1) + 2 * 2 + 3
             if reduce:
                 self._reduce_ready(l)
         self._join_side()
