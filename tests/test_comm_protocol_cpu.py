@@ -143,3 +143,39 @@ def test_bucket_size_grows_until_the_plan_fits_the_signal_pad():
             size *= 2
     assert len(buckets) <= MAX_BUCKETS and sum(b.n for b in buckets) == total
     assert buckets[0].ready_key < 99     # several layers share the first bucket
+
+
+@pytest.mark.parametrize("preset", ["gpt2-124m", "gpt2-350m", "gpt2-1.5b"])
+def test_bucket_and_range_plan_covers_every_preset_at_every_world(preset):
+    """For the real parameter layouts: at 2, 4 and 8 ranks every rank's ranges tile the flat buffer in
+    units of 8 elements, every element of a two-shot bucket has exactly one owner and every element of
+    a one-shot bucket is kept by all ranks."""
+    import torch
+    from zero_to_hero_b200.config import get_preset
+    from zero_to_hero_b200.engine import ParamLayout
+    cfg = get_preset(preset)
+    lay = ParamLayout(cfg.model)
+    groups = lay.backward_groups(cfg.model.num_layers)
+    bucket_bytes = 32 << 20
+    while True:  # what FusedDDP.setup does: grow the bucket size until the count fits
+        try:
+            buckets = plan_buckets(lay.total, groups, bucket_bytes, 512 << 10)
+            break
+        except ValueError:
+            bucket_bytes *= 2
+    one_shot = torch.zeros(lay.total, dtype=torch.bool)
+    for b in buckets:
+        if b.one_shot:
+            one_shot[b.off:b.off + b.n] = True
+    for world in (2, 4, 8):
+        owners = torch.zeros(lay.total, dtype=torch.int16)
+        for rank in range(world):
+            ranges, _, _ = plan_ranges(buckets, lay.total, world, rank)
+            pos = 0
+            for rg in sorted(ranges, key=lambda x: x.goff):
+                assert rg.goff == pos and rg.n % 8 == 0 and rg.goff % 8 == 0, (world, rank, rg)
+                pos += rg.n
+                if rg.kind != RANGE_ZERO:
+                    owners[rg.goff:rg.goff + rg.n] += 1
+            assert pos == lay.total
+        assert bool((owners[~one_shot] == 1).all()) and bool((owners[one_shot] == world).all())
