@@ -3,6 +3,7 @@ the held-out validation split of a token file, per-rank loader state in checkpoi
 import json
 import socket
 
+import pytest
 import torch
 
 from zero_to_hero_b200.config import get_preset
@@ -96,3 +97,42 @@ def test_per_rank_loader_states_round_trip():
     got = [ld.next_host_batch()[0] for ld in fresh]
     assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
     assert not torch.equal(got[0], got[1])
+    with pytest.raises(ValueError):
+        select_rank_state(saved, 0, 3)
+
+
+def test_elastic_resume_reshards_the_token_stream(tmp_path):
+    """A checkpoint of a 4-rank job resumed by 2 ranks (and by 8): with `elastic` the token-file
+    loaders carry on where the old job's stream stood, each new rank on its own stride, so nothing
+    already consumed is read again and nothing is skipped."""
+    import numpy as np
+    from zero_to_hero_b200.data.text import TokenFileLoader
+    path = tmp_path / "tokens.bin"
+    np.arange(40000, dtype=np.uint16).tofile(path)  # token value == position in the file
+    B, T = 2, 16
+    span = B * T
+    old = [TokenFileLoader(path, B, T, rank=r, world_size=4) for r in range(4)]
+    for _ in range(3):
+        for ld in old:
+            ld.next_host_batch()
+    consumed = 3 * 4 * span
+    saved = {"world": 4, "per_rank": [ld.state() for ld in old]}
+    for new_world in (2, 8):
+        new = [TokenFileLoader(path, B, T, rank=r, world_size=new_world) for r in range(new_world)]
+        for r, ld in enumerate(new):
+            ld.load_state(select_rank_state(saved, r, new_world, elastic=True))
+        firsts = [int(ld.next_host_batch()[0][0, 0]) for ld in new]
+        assert firsts == [consumed + r * span for r in range(new_world)]
+        seconds = [int(ld.next_host_batch()[0][0, 0]) for ld in new]
+        assert seconds == [consumed + (new_world + r) * span for r in range(new_world)]
+    # the synthetic loader: surviving ranks keep their generators, so their streams continue
+    syn = [SyntheticLoader("train", 2, 16, 100, "cpu", r, 4, seed=7) for r in range(4)]
+    for ld in syn:
+        ld.next_host_batch()
+    saved = {"world": 4, "per_rank": [ld.state() for ld in syn]}
+    want = [ld.next_host_batch()[0] for ld in syn[:2]]
+    fresh = [SyntheticLoader("train", 2, 16, 100, "cpu", r, 2, seed=7) for r in range(2)]
+    for r, ld in enumerate(fresh):
+        ld.load_state(select_rank_state(saved, r, 2, elastic=True))
+    got = [ld.next_host_batch()[0] for ld in fresh]
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])

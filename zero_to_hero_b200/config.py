@@ -68,6 +68,9 @@ class TrainConfig:
     hellaswag: str = ""         # JSONL of pre-tokenised HellaSwag examples; scored at eval time
     checkpoint_dir: str = ""
     checkpoint_interval: int = 0
+    # resume a checkpoint written by a job with another number of ranks: parameters and moments load
+    # into any world size, the data cursors are re-sharded (engine.select_rank_state)
+    elastic_resume: bool = False
     use_cuda_graph: bool = True
     overlap_wgrad: bool = True  # weight-gradient GEMMs on a second stream (fills the tails of the data-gradient chain)
     log_jsonl: str = ""

@@ -21,6 +21,7 @@ class SyntheticLoader:
         salt = {"train": 0, "val": 1}.get(split, 2)
         # validation is not sharded (nn/gpt2/train_ddp.py:77); training is, by rank
         r = rank if split == "train" else 0
+        self._rank = r
         self.gen = torch.Generator(device="cpu").manual_seed(seed + 1000003 * salt + 7919 * r)
         self.pin = (self.device.type == "cuda") if pin is None else pin
         self.cursor = 0
@@ -45,5 +46,13 @@ class SyntheticLoader:
         return {"cursor": self.cursor, "rng": self.gen.get_state()}
 
     def load_state(self, st: dict) -> None:
+        if st.get("reshard"):
+            # another job size: a rank that existed before carries on with that rank's generator, a
+            # new rank keeps the fresh stream of its own index; all take the furthest cursor
+            states = st["per_rank"]
+            self.cursor = max(int(s["cursor"]) for s in states)
+            if self._rank < len(states):
+                self.gen.set_state(states[self._rank]["rng"])
+            return
         self.cursor = st["cursor"]
         self.gen.set_state(st["rng"])

@@ -83,4 +83,13 @@ class TokenFileLoader:
         return {"cursor": self.cursor}
 
     def load_state(self, st):
+        if st.get("reshard"):
+            # Saved by a job of another size. Rank r of W ranks sits at r*span + k*span*W after k
+            # batches, so the smallest saved cursor, rounded down to a whole global batch of the old
+            # job, is where the stream as a whole stands; this rank takes its own stride from there.
+            old_world = int(st["old_world"])
+            lowest = min(int(s["cursor"]) for s in st["per_rank"])
+            consumed = lowest - lowest % (self.span * old_world)
+            self.cursor = consumed + self.rank * self.span
+            return
         self.cursor = st["cursor"]

@@ -762,10 +762,13 @@ def save_engine_checkpoint(engine: GPT2TrainEngine, path, data_state=None) -> No
         dist.barrier()
 
 
-def load_engine_checkpoint(engine: GPT2TrainEngine, path) -> dict:
+def load_engine_checkpoint(engine: GPT2TrainEngine, path, elastic: bool = False) -> dict:
     """Restores parameters, moments, step, dropout counters and RNG; returns the checkpoint with
-    `ck["data"]` replaced by THIS rank's loader state (raises if the job's world size differs
-    from the one that wrote the data cursors)."""
+    `ck["data"]` replaced by THIS rank's loader state. Parameters and moments are stored whole, so
+    they load into any number of ranks; the data cursors are per rank. If the job's world size
+    differs from the one that wrote them this raises, unless `elastic` is set (a job that goes on
+    with the ranks it has left, or was given more): the loader then gets all saved states and
+    re-shards them itself (`select_rank_state`)."""
     from .utils.checkpoint import load_checkpoint, set_rng_state
 
     ck = load_checkpoint(path)
@@ -785,14 +788,21 @@ def load_engine_checkpoint(engine: GPT2TrainEngine, path) -> dict:
             engine.drop_seed.fill_(engine.drop_seed0 + advanced)
             engine.micro_steps_done = int(opt.get("micro_steps_done", 0))
     set_rng_state(ck["rng"])
-    ck["data"] = select_rank_state(ck.get("data"), engine.rank, engine.world)
+    ck["data"] = select_rank_state(ck.get("data"), engine.rank, engine.world, elastic=elastic)
     return ck
 
 
-def select_rank_state(data, rank: int, world: int):
-    """This rank's entry of the per-rank loader states a checkpoint holds."""
+def select_rank_state(data, rank: int, world: int, elastic: bool = False):
+    """This rank's entry of the per-rank loader states a checkpoint holds. With another world size:
+    an error, or with `elastic` a `{"reshard": True, "old_world": W, "per_rank": [...]}` record that
+    the loaders' `load_state` turns into a position of their own (the token-file loader continues
+    the global stream where the old job stopped, re-strided for the new rank count; the synthetic
+    loader keeps the generator of the old rank with the same index, or starts a fresh stream)."""
     if not isinstance(data, dict) or "per_rank" not in data:
         return data  # a single-state checkpoint of a one-rank job
     if int(data["world"]) != world:
-        raise ValueError(f"checkpoint holds data cursors of {data['world']} ranks; this job has {world}")
+        if not elastic:
+            raise ValueError(f"checkpoint holds data cursors of {data['world']} ranks; this job has {world} "
+                             "(train.elastic_resume=true re-shards them)")
+        return {"reshard": True, "old_world": int(data["world"]), "per_rank": list(data["per_rank"])}
     return data["per_rank"][rank]

@@ -110,7 +110,7 @@ def train(cfg: Config, resume: str = "") -> dict:
         eng = GPT2TrainEngine(cfg, device, comm=comm)
         start = 0
         if resume:
-            ck = load_engine_checkpoint(eng, resume)
+            ck = load_engine_checkpoint(eng, resume, elastic=tc.elastic_resume)
             start = int(ck["step"])
             if ck.get("data") and hasattr(loader, "load_state"):
                 loader.load_state(ck["data"])  # this rank's own cursor / generator state
