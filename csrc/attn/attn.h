@@ -28,4 +28,10 @@ int flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const fl
                     float* dq_accum, float* stats, int B, int T, int H, float drop_p,
                     const unsigned long long* seed_ptr, unsigned int site, float* dbias, int* status,
                     cudaStream_t stream);
+// ordered != 0: the KV tiles are launched one after the other so that the fp32 dQ accumulation happens
+// in a fixed order (bitwise reproducible results; dbias must be null).
+int flash_bwd_ex(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                 float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                 const unsigned long long* seed_ptr, unsigned int site, float* dbias, int ordered, int* status,
+                 cudaStream_t stream);
 }  // namespace z2h

@@ -78,6 +78,10 @@ struct BwdParams {
   // QKV projection's bias; the dK / dV thirds by this kernel's epilogue, the dQ third by the
   // conversion kernel
   float* dbias;
+  // >= 0: this launch covers only KV tile j_fixed of every (batch, head) (grid = B * H). The host then
+  // launches the tiles one after the other, so the additions to the fp32 dQ buffer happen in KV-tile
+  // order whatever the CTA scheduling: the bitwise reproducible form, about 1.5 x slower.
+  int j_fixed;
   // attention-probability dropout (DROP instantiation only), same stream as the forward kernel
   float drop_p;
   const unsigned long long* seed_ptr;
@@ -121,8 +125,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = (p.T + TS - 1) / TS;
   // KV tile 0 has the most query tiles to visit: schedule it first
-  const int j = (int)(blockIdx.x % n_t);
-  const int bh = blockIdx.x / n_t;
+  const int j = p.j_fixed >= 0 ? p.j_fixed : (int)(blockIdx.x % n_t);
+  const int bh = p.j_fixed >= 0 ? (int)blockIdx.x : (int)(blockIdx.x / n_t);
   const int h = bh % p.H, b = bh / p.H;
   const int row0 = b * p.T;
   const int n_iter = n_t - j;
@@ -641,7 +645,16 @@ int flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const fl
                     float* dq_accum, float* stats, int B, int T, int H, float drop_p,
                     const unsigned long long* seed_ptr, unsigned int site, float* dbias, int* status,
                     cudaStream_t stream) {
+  return flash_bwd_ex(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site, dbias, 0,
+                      status, stream);
+}
+
+int flash_bwd_ex(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                 float* dq_accum, float* stats, int B, int T, int H, float drop_p,
+                 const unsigned long long* seed_ptr, unsigned int site, float* dbias, int ordered, int* status,
+                 cudaStream_t stream) {
   const int C = H * HD;
+  if (ordered && dbias != nullptr) return 1;  // the bias by-product is accumulated with atomics
   if (!(drop_p >= 0.f) || drop_p >= 1.f) return 1;
   if (B <= 0 || T <= 0) return 0;
   const int Tpad = (T + TS - 1) / TS * TS;
@@ -676,8 +689,17 @@ int flash_bwd_dbias(const void* qkv, const void* out, const void* dout, const fl
     cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   }
   const int n_t = (T + TS - 1) / TS;
-  launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H * n_t),
-                dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm_qkv, tm_do, p);
+  if (ordered) {
+    for (int jt = 0; jt < n_t; ++jt) {
+      p.j_fixed = jt;
+      launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H),
+                    dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm_qkv, tm_do, p);
+    }
+  } else {
+    p.j_fixed = -1;
+    launch_kernel(drop_p > 0.f ? flash_bwd_kernel<true> : flash_bwd_kernel<false>, dim3(B * H * n_t),
+                  dim3(NUM_THREADS), SMEM_BYTES, stream, true, tm_qkv, tm_do, p);
+  }
   {
     const long long total = (((long long)B * T + 31) / 32) * H * 4 * 32;
     const int grid = (int)((total + 255) / 256);
@@ -708,6 +730,13 @@ extern "C" int z2h_flash_bwd_dbias(const void* qkv, const void* out, const void*
                                    float* dbias, int* status, void* stream) {
   return z2h::flash_bwd_dbias(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site,
                               dbias, status, (cudaStream_t)stream);
+}
+extern "C" int z2h_flash_bwd_ex(const void* qkv, const void* out, const void* dout, const float* lse,
+                                void* dqkv, float* dq_accum, float* stats, int B, int T, int H,
+                                float drop_p, const unsigned long long* seed_ptr, unsigned int site,
+                                float* dbias, int ordered, int* status, void* stream) {
+  return z2h::flash_bwd_ex(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p, seed_ptr, site, dbias,
+                           ordered, status, (cudaStream_t)stream);
 }
 extern "C" long long z2h_flash_bwd_dq_elems(int B, int T, int H) {
   return (((long long)B * T + 31) / 32 * 32) * H * 64;

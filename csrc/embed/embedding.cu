@@ -75,6 +75,60 @@ __global__ void embed_bwd_wte_kernel(const IdxT* __restrict__ idx, const __nv_bf
   }
 }
 
+// The same sums in a fixed order, for bitwise reproducible training: one warp per vocabulary row scans
+// the token ids (staged through shared memory, 2048 at a time, for the CTA's eight rows) and adds the
+// rows of dx whose token is its own in ascending position; one writer per row, no atomics. Most rows
+// have no occurrence and cost only the scan (M / 32 ballots). Slower than the scatter above (the ids
+// are read V / 8 times), which is why it is a mode, not the default.
+constexpr int kOrderedChunk = 2048;
+template <typename IdxT>
+__global__ void __launch_bounds__(256)
+embed_bwd_wte_ordered_kernel(const IdxT* __restrict__ idx, const __nv_bfloat16* __restrict__ dx,
+                             float* __restrict__ dwte, int M, int C, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int sidx[kOrderedChunk];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int v = blockIdx.x * 8 + warp;  // this warp's vocabulary row (may be past the end)
+  for (int c0 = 0; c0 < C; c0 += 32 * 8) {  // 256 columns per pass: 8 per lane
+    const int c = c0 + lane * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    bool any = false;
+    for (int base = 0; base < M; base += kOrderedChunk) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < kOrderedChunk && base + i < M; i += blockDim.x) {
+        long long tok = (long long)idx[base + i];
+        sidx[i] = (int)(tok < 0 ? 0 : (tok >= V ? V - 1 : tok));
+      }
+      __syncthreads();
+      const int n = min(kOrderedChunk, M - base);
+      for (int i0 = 0; i0 < n; i0 += 32) {
+        const bool mine = (i0 + lane < n) && sidx[i0 + lane] == v;
+        unsigned hits = __ballot_sync(0xffffffffu, mine);
+        while (hits != 0u) {  // ascending position: the order of the additions is fixed
+          const int b = __ffs(hits) - 1;
+          hits &= hits - 1u;
+          any = true;
+          if (c < C) {
+            const uint4 a = *reinterpret_cast<const uint4*>(dx + (long long)(base + i0 + b) * C + c);
+            const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z),
+                         a3 = unpack_bf16x2(a.w);
+            acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y;
+            acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+          }
+        }
+      }
+    }
+    if (any && v < V && c < C) {
+      float* dst = dwte + (long long)v * C + c;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] += acc[j];
+    }
+  }
+}
+
 __global__ void embed_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dx, float* __restrict__ dwpe,
                                      int B, int T, int C) {
   pdl_launch_dependents();
@@ -109,12 +163,25 @@ int embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, 
 
 int embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B, int T,
               int C, int V, cudaStream_t stream) {
+  return embed_bwd_ordered(idx, idx_is_64, dx, dwte, dwpe, B, T, C, V, 0, stream);
+}
+
+int embed_bwd_ordered(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B, int T,
+                      int C, int V, int ordered, cudaStream_t stream) {
   if (C % 8 != 0) return 1;
   const int M = B * T;
   if (M <= 0) return 0;
   const long long total = (long long)M * (C / 4);
   const int grid = (int)((total + 255) / 256 < sm_count_current_device() * 16 ? (total + 255) / 256 : sm_count_current_device() * 16);
-  if (idx_is_64)
+  if (ordered) {
+    const int g = (V + 7) / 8;
+    if (idx_is_64)
+      launch_kernel(embed_bwd_wte_ordered_kernel<long long>, dim3(g), dim3(256), 0, stream, true, (const long long*)idx,
+                    (const __nv_bfloat16*)dx, dwte, M, C, V);
+    else
+      launch_kernel(embed_bwd_wte_ordered_kernel<int>, dim3(g), dim3(256), 0, stream, true, (const int*)idx,
+                    (const __nv_bfloat16*)dx, dwte, M, C, V);
+  } else if (idx_is_64)
     launch_kernel(embed_bwd_wte_kernel<long long>, dim3(grid), dim3(256), 0, stream, true, (const long long*)idx,
                                                              (const __nv_bfloat16*)dx, dwte, M, C, V);
   else
@@ -134,6 +201,10 @@ extern "C" {
 int z2h_embed_fwd(const void* idx, int idx_is_64, const void* wte, const void* wpe, void* out, int M,
                   int T, int C, int V, int* status, void* stream) {
   return z2h::embed_fwd(idx, idx_is_64, wte, wpe, out, M, T, C, V, status, (cudaStream_t)stream);
+}
+int z2h_embed_bwd_ordered(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B,
+                          int T, int C, int V, int ordered, void* stream) {
+  return z2h::embed_bwd_ordered(idx, idx_is_64, dx, dwte, dwpe, B, T, C, V, ordered, (cudaStream_t)stream);
 }
 int z2h_embed_bwd(const void* idx, int idx_is_64, const void* dx, float* dwte, float* dwpe, int B,
                   int T, int C, int V, void* stream) {

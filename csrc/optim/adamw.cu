@@ -186,9 +186,17 @@ int adamw_step(float* p32, float* g, float* m, float* v, void* p16, long long n,
 
 int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                 cudaStream_t stream) {
+  return colsum_bf16_ordered(dy, M, N, ld, db, accumulate, 0, stream);
+}
+
+// ordered != 0: one slab, i.e. every column is summed by one CTA in a fixed order and added to db by
+// a single writer, so the result does not depend on the order in which CTAs finish (slower: N / 256
+// CTAs stream the whole matrix).
+int colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
+                        cudaStream_t stream) {
   if (N % 8 != 0 || ld % 8 != 0) return 1;
   if (!accumulate) cudaMemsetAsync(db, 0, sizeof(float) * N, stream);
-  int slabs = (M + 127) / 128;
+  int slabs = ordered ? 1 : (M + 127) / 128;
   if (slabs > 128) slabs = 128;
   if (slabs < 1) slabs = 1;
   const int rows_per_slab = (M + slabs - 1) / slabs;
@@ -214,6 +222,10 @@ int z2h_adamw_step(float* p32, float* g, float* m, float* v, void* p16, long lon
                    int zero_grad, void* stream) {
   return z2h::adamw_step(p32, g, m, v, p16, n, n_decay, hyper, partials, num_partials, norm_out,
                          zero_grad, (cudaStream_t)stream);
+}
+int z2h_colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
+                            void* stream) {
+  return z2h::colsum_bf16_ordered(dy, M, N, ld, db, accumulate, ordered, (cudaStream_t)stream);
 }
 int z2h_colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                     void* stream) {

@@ -30,6 +30,8 @@ int adamw_step(float* p32, float* g, float* m, float* v, void* p16, long long n,
                int zero_grad, cudaStream_t stream);
 
 // db[n] (+)= sum_m dy[m, n]; dy is bf16 [M, ld].
+int colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
+                        cudaStream_t stream);
 int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                 cudaStream_t stream);
 

@@ -328,3 +328,36 @@ def test_train_loop_with_eval_hellaswag_checkpoint_and_resume(tmp_path):
     assert [h["step"] for h in resumed["history"]] == [2, 3]
     # step 2 of the resumed run repeats step 2 of the first run (same weights, moments, data cursor)
     assert resumed["history"][0]["train"] == pytest.approx(hist[2]["train"], abs=2e-3)
+
+
+@pytest.mark.parametrize("dropout", [0.0, 0.1])
+def test_deterministic_mode_repeats_training_bit_for_bit(dropout):
+    """`train.deterministic=true`: two engines from the same seed on the same batches end three steps
+    with bitwise equal master weights, moments, losses and gradient norms (weight gradients without
+    split-K, dQ accumulated one KV tile per launch, bias and embedding gradients by single writers),
+    and they track the default mode's result to rounding."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from zero_to_hero_b200.engine import GPT2TrainEngine
+    from zero_to_hero_b200.ops import _lib
+
+    def run(deterministic):
+        cfg = _cfg()
+        cfg.model.dropout = dropout
+        cfg.train.deterministic = deterministic
+        eng = GPT2TrainEngine(cfg, "cuda", seed=3)
+        g = torch.Generator().manual_seed(5)
+        losses = []
+        for _ in range(3):
+            eng.train_step(_batches(g), lr=1e-3)
+            losses.append((eng.read_loss(), eng.read_grad_norm()))
+        return eng.p32.clone(), eng.m.clone(), eng.v.clone(), losses
+
+    a, b, plain = run(True), run(True), run(False)
+    assert a[3] == b[3]
+    for x, y in zip(a[:3], b[:3]):
+        assert torch.equal(x, y)
+    # same mathematics as the default mode
+    assert a[3][-1][0] == pytest.approx(plain[3][-1][0], abs=2e-3)
+    assert (a[0] - plain[0]).abs().max().item() < 2.5e-3 * 3
+    _lib.check_status()

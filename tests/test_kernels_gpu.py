@@ -561,3 +561,52 @@ def test_mma_probe_reports_sane_costs(dev):
     ts64 = probe(5, 64, 0)["done_cycles_per_mma"]
     assert 20 < ts64 < n64 < n256 < 400, (ts64, n64, n256)
     status_ok()
+
+
+def test_ordered_kernels_repeat_bit_for_bit_and_match_the_default_ones(dev):
+    """The fixed-order variants behind `train.deterministic`: embedding backward (one writer per
+    vocabulary row, ascending position), column sums (one CTA per column block), attention backward
+    (one KV tile per launch). Each equals the default kernel to rounding and itself bit for bit."""
+    from zero_to_hero_b200.ops import native as N
+    torch.manual_seed(11)
+    # embedding: many repeats of few tokens, a vocabulary that is not a multiple of 8, C > 256
+    B, T, C, V = 4, 300, 776, 203
+    idx = torch.randint(0, 37, (B, T), device=dev)
+    idx[0, :5] = V - 1
+    dx = torch.randn(B * T, C, device=dev).bfloat16()
+    ref = torch.zeros(V, C, device=dev).index_add_(0, idx.reshape(-1), dx.float())
+    outs = []
+    for _ in range(2):
+        dwte = torch.zeros(V, C, device=dev)
+        dwpe = torch.zeros(T, C, device=dev)
+        N.embed_bwd(idx, dx, dwte, dwpe, B, T, ordered=True)
+        outs.append(dwte)
+    assert rel_err(outs[0], ref) < 1e-5 and torch.equal(outs[0], outs[1])
+    # column sums
+    dy = torch.randn(5000, 2304, device=dev).bfloat16()
+    sums = []
+    for _ in range(2):
+        db = torch.ones(2304, device=dev)
+        N.colsum_bf16(dy, db, ordered=True)
+        sums.append(db)
+    assert rel_err(sums[0], 1 + dy.float().sum(0)) < 1e-5 and torch.equal(sums[0], sums[1])
+    # attention backward
+    B, T, H = 2, 520, 3
+    C = H * 64
+    qkv = (torch.randn(B * T, 3 * C, device=dev) * 0.7).bfloat16()
+    out = torch.empty(B * T, C, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev)
+    N.flash_fwd(qkv, out, lse, B, T, H)
+    dout = (torch.randn(B * T, C, device=dev) * 0.5).bfloat16()
+    dqa = torch.empty(N.flash_bwd_dq_elems(B, T, H), device=dev)
+    stats = torch.empty(N.flash_bwd_stats_elems(B, T, H), device=dev)
+    plain = torch.zeros_like(qkv)
+    N.flash_bwd(qkv, out, dout, lse, plain, dqa, stats, B, T, H)
+    grads = []
+    for _ in range(2):
+        d = torch.zeros_like(qkv)
+        N.flash_bwd(qkv, out, dout, lse, d, dqa, stats, B, T, H, ordered=True)
+        grads.append(d)
+    assert torch.equal(grads[0], grads[1])
+    assert rel_err(grads[0], plain) < 2e-3
+    status_ok()

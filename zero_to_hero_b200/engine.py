@@ -181,6 +181,7 @@ class GPT2TrainEngine:
         self._comm_stream = torch.cuda.Stream(device=self.device)
         self._side_done = []
         self._overlap = False
+        self.deterministic = bool(cfg.train.deterministic)
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self._reduced_in_backward = False
         self._n = 0
@@ -300,7 +301,8 @@ class GPT2TrainEngine:
         out = self.gw(name)
         n_out, k_in = out.shape
         tiles = math.ceil(n_out / 128) * math.ceil(k_in / 256)
-        sk = pick_split_k(tiles, math.ceil(dy.shape[0] / 64))
+        # split-K pieces meet in atomics; the reproducible mode takes whole tiles (in-place fp32 add)
+        sk = 1 if self.deterministic else pick_split_k(tiles, math.ceil(dy.shape[0] / 64))
         if sk == 1:
             G.gemm(dy, x, out, a_mn=True, b_mn=True, epi=G.EPI_ACCUMULATE)
         else:
@@ -473,7 +475,7 @@ class GPT2TrainEngine:
             def wg_mlp_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
                 if not fuse_db:
-                    N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"))
+                    N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"), ordered=self.deterministic)
 
             self._on_side(wg_mlp_proj)
             # The c_fc bias gradient is the column sum of d_4c: a by-product of this GEMM's epilogue
@@ -481,7 +483,8 @@ class GPT2TrainEngine:
             # pass on the side stream it makes no measurable difference to the 124M step (950.3-952.6 k
             # tokens/s with it, 950.0-957.3 k without, alternating runs on one box) and saves a launch
             # per layer; Z2H_FC_BIAS_IN_GEMM=0 brings the separate pass back.
-            fc_db_in_gemm = self.M % 32 == 0 and os.environ.get("Z2H_FC_BIAS_IN_GEMM", "1") != "0"
+            fc_db_in_gemm = (self.M % 32 == 0 and os.environ.get("Z2H_FC_BIAS_IN_GEMM", "1") != "0"
+                             and not self.deterministic)  # the by-product is added with atomics
             G.gemm(dy, w(p + "mlp.c_proj.weight"), self.d_4c, b_mn=True,
                    aux_in=self.pre[l], epi=G.EPI_MUL_AUX,
                    colsum=gw(p + "mlp.c_fc.bias") if fc_db_in_gemm else None)
@@ -489,7 +492,7 @@ class GPT2TrainEngine:
             def wg_mlp_fc(l=l, p=p, fc_db_in_gemm=fc_db_in_gemm):
                 self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
                 if not fc_db_in_gemm:
-                    N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"))
+                    N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"), ordered=self.deterministic)
 
             self._on_side(wg_mlp_fc)
             G.gemm(self.d_4c, w(p + "mlp.c_fc.weight"), self.d_c, b_mn=True)
@@ -508,16 +511,22 @@ class GPT2TrainEngine:
             def wg_attn_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
                 if not fuse_db:
-                    N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"))
+                    N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"), ordered=self.deterministic)
 
             self._on_side(wg_attn_proj)
             G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
-            # the c_attn bias gradient (column sums of d_qkv) comes out of the attention kernels
+            # the c_attn bias gradient (column sums of d_qkv) comes out of the attention kernels; in
+            # the reproducible mode the attention backward runs one KV tile per launch (dQ accumulates
+            # in a fixed order) and the bias gradient is a single-writer column sum
+            det = self.deterministic
             N.flash_bwd(self.qkv[l], self.att[l], self.d_c, self.lse[l], self.d_qkv, self.dq_accum,
-                        self.attn_stats, B, T, H, pd, seed, 1 + 3 * l, dbias=gw(p + "attn.c_attn.bias"))
+                        self.attn_stats, B, T, H, pd, seed, 1 + 3 * l,
+                        dbias=None if det else gw(p + "attn.c_attn.bias"), ordered=det)
 
-            def wg_attn_qkv(l=l, p=p):
+            def wg_attn_qkv(l=l, p=p, det=det):
                 self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
+                if det:
+                    N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"), ordered=True)
 
             self._on_side(wg_attn_qkv)
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)
@@ -530,7 +539,9 @@ class GPT2TrainEngine:
             # dgrad GEMMs, column-sum launches (the projection biases ride in the LayerNorm backward
             # without dropout, the QKV bias in the attention kernels, the c_fc bias usually in its
             # GEMM), LN bwd (2 kernels each), flash bwd (3)
-            self._n += 4 + (0 if fuse_db else 2) + (0 if fc_db_in_gemm else 1) + 2 * 2 + 3
+            # (reproducible mode: the attention backward is one launch per KV tile, plus the QKV column sum)
+            self._n += 4 + (0 if fuse_db else 2) + (0 if fc_db_in_gemm else 1) + 2 * 2
+            self._n += (2 + (T + 127) // 128 + 1) if det else 3
             if reduce:
                 self._reduce_ready(l)
         self._join_side()
@@ -538,7 +549,7 @@ class GPT2TrainEngine:
             N.dropout_apply(R[cur], R[cur], pd, seed, 0)
             self._n += 1
         N.embed_bwd(self.idx, R[cur], gw("transformer.wte.weight"),
-                    gw("transformer.wpe.weight"), B, T)
+                    gw("transformer.wpe.weight"), B, T, ordered=self.deterministic)
         self._n += 2
         if reduce:
             self._reduce_ready(-1)

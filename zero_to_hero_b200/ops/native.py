@@ -23,6 +23,11 @@ _sigs = {
                       c_void_p, c_void_p],
     "z2h_embed_bwd": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_void_p],
+    "z2h_embed_bwd_ordered": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p],
+    "z2h_colsum_bf16_ordered": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "z2h_flash_bwd_ex": [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_void_p, ctypes.c_uint,
+                         c_void_p, c_int, c_void_p, c_void_p],
     "z2h_ce_fwd_bwd": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_longlong,
                        c_float, c_int, c_int, c_void_p],
     "z2h_reduce_sum": [c_void_p, c_int, c_float, c_void_p, c_int, c_void_p],
@@ -99,10 +104,12 @@ def embed_fwd(idx, wte, wpe, out, T):
            "embed_fwd")
 
 
-def embed_bwd(idx, dx, dwte, dwpe, B, T):
+def embed_bwd(idx, dx, dwte, dwpe, B, T, ordered: bool = False):
+    """`ordered`: the token-embedding gradient is summed in ascending position by one writer per
+    vocabulary row instead of with atomics (bitwise reproducible, slower)."""
     C = dx.shape[-1]
-    _check(_f("z2h_embed_bwd")(ptr(idx), _is64(idx), ptr(dx), ptr(dwte), ptr(dwpe), B, T, C,
-                               dwte.shape[0], stream_ptr()), "embed_bwd")
+    _check(_f("z2h_embed_bwd_ordered")(ptr(idx), _is64(idx), ptr(dx), ptr(dwte), ptr(dwpe), B, T, C,
+                                       dwte.shape[0], int(ordered), stream_ptr()), "embed_bwd")
 
 
 def ce_fwd_bwd(logits, targets, losses, v_real, grad_scale, write_grad=True, ignore_index=-100):
@@ -130,10 +137,12 @@ def adamw_step(p32, g, m, v, p16, n_decay, hyper, partials, num_partials, norm_o
                                 int(zero_grad), stream_ptr()), "adamw_step")
 
 
-def colsum_bf16(dy, db, accumulate=True):
+def colsum_bf16(dy, db, accumulate=True, ordered: bool = False):
+    """db (+)= column sums of dy. `ordered`: every column is summed by one CTA in a fixed order (bitwise
+    reproducible, slower) instead of by up to 128 CTAs whose partial sums meet in atomics."""
     M, N = dy.shape
-    _check(_f("z2h_colsum_bf16")(ptr(dy), M, N, dy.stride(0), ptr(db), int(accumulate),
-                                 stream_ptr()), "colsum_bf16")
+    _check(_f("z2h_colsum_bf16_ordered")(ptr(dy), M, N, dy.stride(0), ptr(db), int(accumulate), int(ordered),
+                                         stream_ptr()), "colsum_bf16")
 
 
 def cast_f32_to_bf16(src, dst):
@@ -165,11 +174,22 @@ def flash_bwd_dq_elems(B: int, T: int, H: int) -> int:
 
 
 def flash_bwd(qkv, out, dout, lse, dqkv, dq_accum, stats, B, T, H, drop_p: float = 0.0, seed=None,
-              site: int = 0, dbias=None):
+              site: int = 0, dbias=None, ordered: bool = False):
     """`dbias` (fp32 [3*H*64]): the column sums of `dqkv` as stored are ADDED to it, i.e. the gradient
-    of the QKV projection's bias comes out of the attention backward kernels."""
+    of the QKV projection's bias comes out of the attention backward kernels.
+    `ordered`: the KV tiles are launched one after the other, so the fp32 accumulation of dQ happens in
+    a fixed order (bitwise reproducible, about 1.5x slower; not together with `dbias`)."""
     assert stats.numel() >= flash_bwd_stats_elems(B, T, H)
     assert dq_accum.numel() >= flash_bwd_dq_elems(B, T, H) and dq_accum.dtype == torch.float32
+    if ordered:
+        assert dbias is None, "the bias by-product is accumulated with atomics"
+        if drop_p > 0.0:
+            assert seed is not None and seed.dtype == torch.int64 and seed.is_cuda
+        _check(_f("z2h_flash_bwd_ex")(ptr(qkv), ptr(out), ptr(dout), ptr(lse), ptr(dqkv), ptr(dq_accum),
+                                      ptr(stats), B, T, H, drop_p, ptr(seed) if drop_p > 0.0 else None, site,
+                                      None, 1, ptr(_lib.status_word(out.device)), stream_ptr()),
+               "flash_bwd_ex")
+        return
     if dbias is not None:
         assert dbias.dtype == torch.float32 and dbias.numel() == 3 * H * 64 and dbias.is_contiguous()
         if drop_p > 0.0:
