@@ -17,6 +17,10 @@ enum GemmEpilogue : int {
   // one tanh), so the backward epilogue is one load and one multiply instead of a second GELU'.
   kEpiGeluSaveGrad = 6,  // x = acc (+ bias); aux_out = gelu_tanh'(x); C = gelu_tanh(x)
   kEpiMulAux = 7,        // C = acc * aux_in
+  // Split-K without atomics: K-slice s of a tile is stored (not added) at C + s * slice_stride, fp32;
+  // gemm_fold_slices then adds the slices to their destination in slice order. Together they are the
+  // bitwise reproducible form of a split-K weight gradient.
+  kEpiSliceStore = 8,
 };
 
 // C[M,N] = A * B^T in the logical sense: A is M x K, B is N x K.
@@ -43,6 +47,7 @@ struct GemmArgs {
   // makes the bias gradient of the layer below a by-product of the GEMM that produces that layer's
   // output gradient. Needs a bf16 output, split_k == 1, M % 32 == 0 and N % 32 == 0.
   void* colsum;
+  long long slice_stride;  // kEpiSliceStore: elements between the outputs of consecutive K-slices
   int max_ctas;           // 0 = one CTA per SM
 };
 
@@ -56,6 +61,8 @@ int gemm_bf16_pair(const GemmArgs& args, cudaStream_t stream);
 // 0: always the one-CTA kernel (128 x 256 tiles); 1: the CTA-pair kernel whenever M >= 256;
 // 2 (default): CTA pairs when the problem has at least one 256 x 256 tile per pair of SMs.
 void gemm_set_algo(int algo);
+// dst[i] += slices[0][i] + slices[1][i] + ... (in that order), n elements per slice, n % 4 == 0.
+int gemm_fold_slices(const float* slices, int num_slices, long long n, float* dst, cudaStream_t stream);
 // Stream-K with fix-up in the CTA-pair kernel (balanced k-block runs for tile counts that leave a
 // ragged last wave; see gemm_tcgen05_2cta.cu): 0 off (default: it measured slower), 1 on (also
 // Z2H_GEMM_FIXUP=1).

@@ -24,6 +24,7 @@ struct KernelParams {
   long long ldaux;
   int* status;
   float* colsum;  // fp32 [N] or null: column sums of the (bf16-rounded) output are added here
+  long long slice_stride;  // kEpiSliceStore: elements between the outputs of consecutive K-slices
   int wide;      // every row segment the epilogue touches is 32-byte aligned
   // 0: whole tiles / split-K slices. 1: stream-K, work cut into equal runs of k-blocks, every
   // piece added atomically (fp32 output). 2: stream-K with fix-up (any epilogue, CTA-pair kernel):
@@ -480,11 +481,19 @@ __device__ __forceinline__ void epilogue_block(const KernelParams& p, const uint
 // is handed back (release()) when its last block is in registers.
 //   taddr: tensor-memory address of the warp's first block; active: false for a tile that has no
 //   k-blocks in this worker's share (the accumulator protocol still runs).
+//   k_slice: which K-slice of the tile this is (kEpiSliceStore only; 0 otherwise)
 template <int EPI, bool OUT_FP32, class Release>
-__device__ __forceinline__ void epilogue_stream(const KernelParams& p, uint32_t taddr, long long grow,
+__device__ __forceinline__ void epilogue_stream(const KernelParams& p_in, uint32_t taddr, long long grow,
                                                 int gcol0, const float* sbias, int lane, uint32_t stage,
-                                                bool active, Release release) {
+                                                bool active, int k_slice, Release release) {
   constexpr bool kSecondOperand = EPI == kEpiResidual || EPI == kEpiGeluGrad || EPI == kEpiMulAux;
+  // a K-slice stores to its own copy of the output; a slice without k-blocks stores zeros there
+  KernelParams p_slice = p_in;
+  if (EPI == kEpiSliceStore)
+    p_slice.C = reinterpret_cast<float*>(p_in.C) + (long long)k_slice * p_in.slice_stride;
+  const KernelParams& p = EPI == kEpiSliceStore ? p_slice : p_in;
+  const bool zero_fill = EPI == kEpiSliceStore && !active;
+  if (EPI == kEpiSliceStore) active = true;
   const bool row_ok = active && grow < p.M;
   const bool atomic_interior = OUT_FP32 && EPI == kEpiAtomicAdd && active && sbias == nullptr &&
                                (grow - lane) + 32 <= p.M && gcol0 + 128 <= p.N;
@@ -499,11 +508,19 @@ __device__ __forceinline__ void epilogue_stream(const KernelParams& p, uint32_t 
 #pragma unroll 1
   for (int c = 0; c < 4; c += 2) {
     tmem_ld_wait_for(r[0]);
+    if (zero_fill) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[0][j] = 0u;
+    }
     tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[1]);
     if (kSecondOperand && row_ok && gcol0 + (c + 2) * 32 <= p.N) ld_row(src + (c + 1) * 32, pre[1], wide);
     epilogue_block<EPI, OUT_FP32>(p, r[0], pre[0], grow, gcol0 + c * 32,
                                   sbias != nullptr ? sbias + c * 32 : nullptr, lane, stage, row_ok, atomic_interior);
     tmem_ld_wait_for(r[1]);
+    if (zero_fill) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[1][j] = 0u;
+    }
     if (c + 2 < 4) {
       tmem_ld_32x32b_x32(taddr + (c + 2) * 32, r[0]);
       if (kSecondOperand && row_ok && gcol0 + (c + 3) * 32 <= p.N) ld_row(src + (c + 2) * 32, pre[0], wide);
@@ -522,29 +539,31 @@ __device__ __forceinline__ void epilogue_stream(const KernelParams& p, uint32_t 
 template <class Release>
 __device__ __forceinline__ void epilogue_tile_streamed(const KernelParams& p, uint32_t taddr, long long grow,
                                                        int gcol0, const float* sbias, int lane, uint32_t stage,
-                                                       bool active, Release release) {
+                                                       bool active, int k_slice, Release release) {
   if (p.out_fp32) {
+    if (p.epi == kEpiSliceStore)
+      return epilogue_stream<kEpiSliceStore, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, k_slice, release);
     if (p.epi == kEpiAtomicAdd)
-      return epilogue_stream<kEpiAtomicAdd, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiAtomicAdd, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiAccumulate)
-      return epilogue_stream<kEpiAccumulate, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiAccumulate, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiNone)
-      return epilogue_stream<kEpiNone, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiNone, true>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
   } else {
     if (p.epi == kEpiNone)
-      return epilogue_stream<kEpiNone, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiNone, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiResidual)
-      return epilogue_stream<kEpiResidual, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiResidual, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiGelu)
-      return epilogue_stream<kEpiGelu, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiGelu, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiGeluGrad)
-      return epilogue_stream<kEpiGeluGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiGeluGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiGeluSaveGrad)
-      return epilogue_stream<kEpiGeluSaveGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiGeluSaveGrad, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
     if (p.epi == kEpiMulAux)
-      return epilogue_stream<kEpiMulAux, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+      return epilogue_stream<kEpiMulAux, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
   }
-  return epilogue_stream<kEpiGeneric, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, release);
+  return epilogue_stream<kEpiGeneric, false>(p, taddr, grow, gcol0, sbias, lane, stage, active, 0, release);
 }
 
 // Called before the wait for the accumulator: asks L2 for this lane's 128 columns (256 bytes) of the
@@ -599,6 +618,7 @@ inline KernelParams make_kernel_params(const GemmArgs& g) {
   p.ldaux = g.ldaux;
   p.status = g.status;
   p.colsum = reinterpret_cast<float*>(g.colsum);
+  p.slice_stride = g.slice_stride;
   {
     // 32-byte vectors need 32-byte aligned bases and pitches (bf16: 16 elements, fp32: 8)
     auto a32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };

@@ -227,7 +227,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint64_t* const tempty = &tempty_bar[acc];
       gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
                                           smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
-                                          !empty_split, [tempty] { mbar_arrive(tempty); });
+                                          !empty_split, p.split_k > 1 ? sg.kb0 / sched.kb_per_split : 0,
+                                          [tempty] { mbar_arrive(tempty); });
       if (warp == 2 && lane == 0) Z2H_TRACE();
     }
   }
@@ -287,13 +288,16 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
     return 1;
   if ((g.lda % 8) || (g.ldb % 8) || (g.ldc % 8)) return 1;
   if ((g.epi == kEpiAtomicAdd || g.epi == kEpiAccumulate) && !g.out_fp32) return 1;
-  if (g.split_k > 1 && g.epi != kEpiAtomicAdd) return 1;
+  if (g.split_k > 1 && g.epi != kEpiAtomicAdd && g.epi != kEpiSliceStore) return 1;
+  if (g.epi == kEpiSliceStore && (!g.out_fp32 || g.split_k < 1 || g.bias != nullptr ||
+                                  g.slice_stride < (long long)(g.M - 1) * g.ldc + g.N || (g.slice_stride % 4)))
+    return 1;
   if (g.epi == kEpiResidual && (g.residual == nullptr || (g.ldr % 8))) return 1;
   if (g.epi == kEpiGelu && (g.aux_out == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluGrad && (g.aux_in == nullptr || (g.ldaux % 8))) return 1;
   if (g.epi == kEpiGeluSaveGrad && (g.aux_out == nullptr || (g.ldaux % 8) || g.out_fp32)) return 1;
   if (g.epi == kEpiMulAux && (g.aux_in == nullptr || (g.ldaux % 8) || g.out_fp32)) return 1;
-  if (g.epi < kEpiNone || g.epi > kEpiMulAux) return 1;
+  if (g.epi < kEpiNone || g.epi > kEpiSliceStore) return 1;
   if (reinterpret_cast<uintptr_t>(g.bias) & 7) return 1;
   if (g.colsum != nullptr && (g.out_fp32 || g.split_k != 1 || (g.M % 32) || (g.N % 32) ||
                               (reinterpret_cast<uintptr_t>(g.colsum) & 3)))
@@ -325,12 +329,43 @@ extern "C" int z2h_gemm_trace_read(long long* host_out) {
 extern "C" void z2h_gemm_set_algo(int algo) { z2h::gemm_set_algo(algo); }
 extern "C" void z2h_gemm_set_fixup(int on) { z2h::gemm_set_fixup(on); }
 extern "C" int z2h_gemm_get_algo() { return z2h::gemm_get_algo(); }
-// z2h_gemm_bf16 plus the column-sum by-product (see GemmArgs::colsum).
-extern "C" int z2h_gemm_bf16_colsum(const void* A, int a_mn, long long lda, const void* B, int b_mn,
-                                    long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
-                                    int epi, int split_k, const void* bias, const void* residual,
-                                    long long ldr, void* aux_out, const void* aux_in, long long ldaux,
-                                    int* status, int max_ctas, void* colsum, void* stream) {
+namespace z2h {
+namespace {
+__global__ void fold_slices_kernel(const float* __restrict__ slices, int num_slices, long long n4,
+                                   float* __restrict__ dst) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<const float4*>(dst)[i];
+    for (int s = 0; s < num_slices; ++s) {  // slice order: the sum is the same bits every time
+      const float4 v = reinterpret_cast<const float4*>(slices)[(long long)s * n4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(dst)[i] = acc;
+  }
+}
+}  // namespace
+int gemm_fold_slices(const float* slices, int num_slices, long long n, float* dst, cudaStream_t stream) {
+  if (n % 4 != 0 || num_slices < 1 || (reinterpret_cast<uintptr_t>(slices) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst) & 15))
+    return 1;
+  const long long n4 = n / 4;
+  const int grid = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  fold_slices_kernel<<<grid < 1 ? 1 : grid, 256, 0, stream>>>(slices, num_slices, n4, dst);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+}  // namespace z2h
+
+extern "C" int z2h_gemm_fold_slices(const float* slices, int num_slices, long long n, float* dst, void* stream) {
+  return z2h::gemm_fold_slices(slices, num_slices, n, dst, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// z2h_gemm_bf16 plus the column-sum by-product (GemmArgs::colsum) and the K-slice stride of
+// kEpiSliceStore (GemmArgs::slice_stride).
+extern "C" int z2h_gemm_bf16_ex(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                                long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                                int epi, int split_k, const void* bias, const void* residual,
+                                long long ldr, void* aux_out, const void* aux_in, long long ldaux,
+                                int* status, int max_ctas, void* colsum, long long slice_stride, void* stream) {
   z2h::GemmArgs g;
   g.A = A; g.a_mn = a_mn; g.lda = lda;
   g.B = B; g.b_mn = b_mn; g.ldb = ldb;
@@ -341,7 +376,16 @@ extern "C" int z2h_gemm_bf16_colsum(const void* A, int a_mn, long long lda, cons
   g.aux_out = aux_out; g.aux_in = aux_in; g.ldaux = ldaux;
   g.status = status; g.max_ctas = max_ctas;
   g.colsum = colsum;
+  g.slice_stride = slice_stride;
   return z2h::gemm_bf16(g, reinterpret_cast<cudaStream_t>(stream));
+}
+extern "C" int z2h_gemm_bf16_colsum(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                                    long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,
+                                    int epi, int split_k, const void* bias, const void* residual,
+                                    long long ldr, void* aux_out, const void* aux_in, long long ldaux,
+                                    int* status, int max_ctas, void* colsum, void* stream) {
+  return z2h_gemm_bf16_ex(A, a_mn, lda, B, b_mn, ldb, C, ldc, out_fp32, M, N, K, epi, split_k, bias, residual,
+                          ldr, aux_out, aux_in, ldaux, status, max_ctas, colsum, 0, stream);
 }
 extern "C" int z2h_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn,
                              long long ldb, void* C, long long ldc, int out_fp32, int M, int N, int K,

@@ -228,7 +228,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!FIXUP || p.stream_k != 2) {
         gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
                                             smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
-                                            !empty_split, [tempty] { mbar_arrive_leader_relaxed(tempty); });
+                                            !empty_split, p.split_k > 1 ? sg.kb0 / sched.kb_per_split : 0,
+                                            [tempty] { mbar_arrive_leader_relaxed(tempty); });
         if (warp == 2 && lane == 0) Z2H_TRACE();
         continue;
       }

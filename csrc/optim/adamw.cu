@@ -7,6 +7,7 @@
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "optim.h"
+#include "../gemm/gemm.h"  // gemm_fold_slices: ordered sum of partial vectors
 #include "adamw_update.cuh"
 
 namespace z2h {
@@ -89,7 +90,7 @@ adamw_step_kernel(float* __restrict__ p32, float* __restrict__ g, float* __restr
 // block = 32 column-vectors (256 columns) x 8 row lanes
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ dy, int M, int N, long long ld,
-                   float* __restrict__ db, int rows_per_slab) {
+                   float* __restrict__ db, int rows_per_slab, int store_partials) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float sh[8][256];
@@ -137,7 +138,8 @@ colsum_bf16_kernel(const __nv_bfloat16* __restrict__ dy, int M, int N, long long
     float s = 0.f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) s += sh[r][threadIdx.x];
-    atomicAdd(db + col, s);
+    if (store_partials) db[(long long)blockIdx.y * N + col] = s;  // db is the [slabs][N] scratch here
+    else atomicAdd(db + col, s);
   }
 }
 
@@ -186,22 +188,38 @@ int adamw_step(float* p32, float* g, float* m, float* v, void* p16, long long n,
 
 int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                 cudaStream_t stream) {
-  return colsum_bf16_ordered(dy, M, N, ld, db, accumulate, 0, stream);
+  return colsum_bf16_ordered(dy, M, N, ld, db, accumulate, 0, nullptr, stream);
 }
 
-// ordered != 0: one slab, i.e. every column is summed by one CTA in a fixed order and added to db by
-// a single writer, so the result does not depend on the order in which CTAs finish (slower: N / 256
-// CTAs stream the whole matrix).
-int colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
-                        cudaStream_t stream) {
-  if (N % 8 != 0 || ld % 8 != 0) return 1;
-  if (!accumulate) cudaMemsetAsync(db, 0, sizeof(float) * N, stream);
-  int slabs = ordered ? 1 : (M + 127) / 128;
+// ordered != 0: the result does not depend on the order in which CTAs finish. With a scratch buffer of
+// colsum_scratch_elems(M, N) floats the row slabs store their partial sums there and a second kernel
+// adds them to db in slab order; without one a single slab is used (every column summed by one CTA:
+// N / 256 CTAs stream the whole matrix, slow).
+long long colsum_scratch_elems(int M, int N) {
+  int slabs = (M + 127) / 128;
   if (slabs > 128) slabs = 128;
   if (slabs < 1) slabs = 1;
+  return (long long)slabs * N;
+}
+
+int colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
+                        float* scratch, cudaStream_t stream) {
+  if (N % 8 != 0 || ld % 8 != 0) return 1;
+  if (!accumulate) cudaMemsetAsync(db, 0, sizeof(float) * N, stream);
+  const bool two_stage = ordered && scratch != nullptr;
+  int slabs = (ordered && !two_stage) ? 1 : (M + 127) / 128;
+  if (slabs > 128) slabs = 128;
+  if (slabs < 1) slabs = 1;
+  if (two_stage) {
+    const int rows = (M + slabs - 1) / slabs;
+    dim3 g2((N + 255) / 256, slabs);
+    launch_kernel(colsum_bf16_kernel, dim3(g2), dim3(256), 0, stream, true, (const __nv_bfloat16*)dy, M, N, ld, scratch,
+                  rows, 1);
+    return gemm_fold_slices(scratch, slabs, N, db, stream);
+  }
   const int rows_per_slab = (M + slabs - 1) / slabs;
   dim3 grid((N + 255) / 256, slabs);
-  launch_kernel(colsum_bf16_kernel, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)dy, M, N, ld, db, rows_per_slab);
+  launch_kernel(colsum_bf16_kernel, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)dy, M, N, ld, db, rows_per_slab, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
@@ -224,9 +242,10 @@ int z2h_adamw_step(float* p32, float* g, float* m, float* v, void* p16, long lon
                          zero_grad, (cudaStream_t)stream);
 }
 int z2h_colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
-                            void* stream) {
-  return z2h::colsum_bf16_ordered(dy, M, N, ld, db, accumulate, ordered, (cudaStream_t)stream);
+                            float* scratch, void* stream) {
+  return z2h::colsum_bf16_ordered(dy, M, N, ld, db, accumulate, ordered, scratch, (cudaStream_t)stream);
 }
+long long z2h_colsum_scratch_elems(int M, int N) { return z2h::colsum_scratch_elems(M, N); }
 int z2h_colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                     void* stream) {
   return z2h::colsum_bf16(dy, M, N, ld, db, accumulate, (cudaStream_t)stream);

@@ -31,7 +31,8 @@ int adamw_step(float* p32, float* g, float* m, float* v, void* p16, long long n,
 
 // db[n] (+)= sum_m dy[m, n]; dy is bf16 [M, ld].
 int colsum_bf16_ordered(const void* dy, int M, int N, long long ld, float* db, int accumulate, int ordered,
-                        cudaStream_t stream);
+                        float* scratch, cudaStream_t stream);
+long long colsum_scratch_elems(int M, int N);
 int colsum_bf16(const void* dy, int M, int N, long long ld, float* db, int accumulate,
                 cudaStream_t stream);
 

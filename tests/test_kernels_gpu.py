@@ -584,12 +584,13 @@ def test_ordered_kernels_repeat_bit_for_bit_and_match_the_default_ones(dev):
     assert rel_err(outs[0], ref) < 1e-5 and torch.equal(outs[0], outs[1])
     # column sums
     dy = torch.randn(5000, 2304, device=dev).bfloat16()
-    sums = []
-    for _ in range(2):
-        db = torch.ones(2304, device=dev)
-        N.colsum_bf16(dy, db, ordered=True)
-        sums.append(db)
-    assert rel_err(sums[0], 1 + dy.float().sum(0)) < 1e-5 and torch.equal(sums[0], sums[1])
+    for scratch in (None, torch.full((N.colsum_scratch_elems(5000, 2304),), float("nan"), device=dev)):
+        sums = []
+        for _ in range(2):
+            db = torch.ones(2304, device=dev)
+            N.colsum_bf16(dy, db, ordered=True, scratch=scratch)  # one slab, or partial rows folded in order
+            sums.append(db)
+        assert rel_err(sums[0], 1 + dy.float().sum(0)) < 1e-5 and torch.equal(sums[0], sums[1])
     # attention backward
     B, T, H = 2, 520, 3
     C = H * 64
@@ -609,4 +610,29 @@ def test_ordered_kernels_repeat_bit_for_bit_and_match_the_default_ones(dev):
         grads.append(d)
     assert torch.equal(grads[0], grads[1])
     assert rel_err(grads[0], plain) < 2e-3
+    status_ok()
+
+
+@pytest.mark.parametrize("split", [2, 5, 8])
+def test_gemm_split_k_without_atomics_repeats_bit_for_bit(dev, split):
+    """K-slices stored to their own copies of the output and folded in slice order: the sum equals the
+    atomic split-K result to rounding and is the same bits on every run (a slice count that leaves the
+    last slice without k-blocks included: it must contribute zeros, not stale memory)."""
+    from zero_to_hero_b200.ops import gemm as G
+    torch.manual_seed(split)
+    K, M, N = 1024 + 64, 520, 776  # weight-gradient layout: A is [K, M], B is [K, N]
+    A = (torch.randn(K, M, device=dev) * 0.5).bfloat16()
+    B = (torch.randn(K, N, device=dev) * 0.5).bfloat16()
+    start = torch.randn(M, N, device=dev)
+    want = start + A.float().t() @ B.float()
+    results = []
+    for _ in range(2):
+        ws = torch.full((split * M * N,), float("nan"), device=dev)
+        G.gemm(A, B, ws[:M * N].view(M, N), a_mn=True, b_mn=True, epi=G.EPI_SLICE_STORE, split_k=split,
+               slice_stride=M * N)
+        out = start.clone()
+        G.fold_slices(ws, split, out)
+        results.append(out)
+    assert torch.equal(results[0], results[1])
+    assert rel_err(results[0], want) < 1e-4
     status_ok()

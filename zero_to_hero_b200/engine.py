@@ -182,6 +182,10 @@ class GPT2TrainEngine:
         self._side_done = []
         self._overlap = False
         self.deterministic = bool(cfg.train.deterministic)
+        self._wgrad_slices = None  # K-slice workspace of the reproducible weight gradients
+        # partial rows of the reproducible column sums (one buffer per stream that runs them)
+        self._colsum_scratch = (torch.empty(N.colsum_scratch_elems(self.M, 4 * mc.emb_dim), device=self.device)
+                                if self.deterministic else None)
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self._reduced_in_backward = False
         self._n = 0
@@ -301,8 +305,18 @@ class GPT2TrainEngine:
         out = self.gw(name)
         n_out, k_in = out.shape
         tiles = math.ceil(n_out / 128) * math.ceil(k_in / 256)
-        # split-K pieces meet in atomics; the reproducible mode takes whole tiles (in-place fp32 add)
-        sk = 1 if self.deterministic else pick_split_k(tiles, math.ceil(dy.shape[0] / 64))
+        sk = pick_split_k(tiles, math.ceil(dy.shape[0] / 64))
+        if sk > 1 and self.deterministic:
+            # split-K pieces normally meet in atomics; here every K-slice is stored to its own copy of
+            # the output and the copies are added in slice order
+            n = out.numel()
+            if self._wgrad_slices is None or self._wgrad_slices.numel() < sk * n:
+                self._wgrad_slices = torch.empty(sk * n, device=self.device)
+            G.gemm(dy, x, self._wgrad_slices[:n].view(n_out, k_in), a_mn=True, b_mn=True,
+                   epi=G.EPI_SLICE_STORE, split_k=sk, slice_stride=n)
+            G.fold_slices(self._wgrad_slices, sk, out)
+            self._n += 2
+            return
         if sk == 1:
             G.gemm(dy, x, out, a_mn=True, b_mn=True, epi=G.EPI_ACCUMULATE)
         else:
@@ -475,7 +489,8 @@ class GPT2TrainEngine:
             def wg_mlp_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.act[l], p + "mlp.c_proj.weight")
                 if not fuse_db:
-                    N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"), ordered=self.deterministic)
+                    N.colsum_bf16(dy, gw(p + "mlp.c_proj.bias"), ordered=self.deterministic,
+                                  scratch=self._colsum_scratch)
 
             self._on_side(wg_mlp_proj)
             # The c_fc bias gradient is the column sum of d_4c: a by-product of this GEMM's epilogue
@@ -492,7 +507,8 @@ class GPT2TrainEngine:
             def wg_mlp_fc(l=l, p=p, fc_db_in_gemm=fc_db_in_gemm):
                 self._wgrad(self.d_4c, self.xn2[l], p + "mlp.c_fc.weight")
                 if not fc_db_in_gemm:
-                    N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"), ordered=self.deterministic)
+                    N.colsum_bf16(self.d_4c, gw(p + "mlp.c_fc.bias"), ordered=self.deterministic,
+                                  scratch=self._colsum_scratch)
 
             self._on_side(wg_mlp_fc)
             G.gemm(self.d_4c, w(p + "mlp.c_fc.weight"), self.d_c, b_mn=True)
@@ -511,7 +527,8 @@ class GPT2TrainEngine:
             def wg_attn_proj(dy=dy, l=l, p=p):
                 self._wgrad(dy, self.att[l], p + "attn.c_proj.weight")
                 if not fuse_db:
-                    N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"), ordered=self.deterministic)
+                    N.colsum_bf16(dy, gw(p + "attn.c_proj.bias"), ordered=self.deterministic,
+                                  scratch=self._colsum_scratch)
 
             self._on_side(wg_attn_proj)
             G.gemm(dy, w(p + "attn.c_proj.weight"), self.d_c, b_mn=True)
@@ -526,7 +543,8 @@ class GPT2TrainEngine:
             def wg_attn_qkv(l=l, p=p, det=det):
                 self._wgrad(self.d_qkv, self.xn1[l], p + "attn.c_attn.weight")
                 if det:
-                    N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"), ordered=True)
+                    N.colsum_bf16(self.d_qkv, gw(p + "attn.c_attn.bias"), ordered=True,
+                                  scratch=self._colsum_scratch)
 
             self._on_side(wg_attn_qkv)
             G.gemm(self.d_qkv, w(p + "attn.c_attn.weight"), self.d_c, b_mn=True)

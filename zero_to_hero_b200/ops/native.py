@@ -25,7 +25,7 @@ _sigs = {
                       c_void_p],
     "z2h_embed_bwd_ordered": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                               c_int, c_void_p],
-    "z2h_colsum_bf16_ordered": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "z2h_colsum_bf16_ordered": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "z2h_flash_bwd_ex": [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_void_p, ctypes.c_uint,
                          c_void_p, c_int, c_void_p, c_void_p],
     "z2h_ce_fwd_bwd": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_longlong,
@@ -137,12 +137,21 @@ def adamw_step(p32, g, m, v, p16, n_decay, hyper, partials, num_partials, norm_o
                                 int(zero_grad), stream_ptr()), "adamw_step")
 
 
-def colsum_bf16(dy, db, accumulate=True, ordered: bool = False):
-    """db (+)= column sums of dy. `ordered`: every column is summed by one CTA in a fixed order (bitwise
-    reproducible, slower) instead of by up to 128 CTAs whose partial sums meet in atomics."""
+def colsum_scratch_elems(M: int, N: int) -> int:
+    """fp32 elements of scratch the ordered column sum of an M x N matrix uses (up to 128 partial rows)."""
+    return min(128, max(1, (M + 127) // 128)) * N
+
+
+def colsum_bf16(dy, db, accumulate=True, ordered: bool = False, scratch=None):
+    """db (+)= column sums of dy. By default up to 128 row slabs are summed by CTAs of their own and
+    meet in atomics. `ordered`: bitwise reproducible; with `scratch` (fp32, colsum_scratch_elems) the
+    slabs store their partial sums there and a second kernel adds them in slab order, without it one CTA
+    sums a whole column block (slow)."""
     M, N = dy.shape
+    if scratch is not None:
+        assert scratch.dtype == torch.float32 and scratch.numel() >= colsum_scratch_elems(M, N)
     _check(_f("z2h_colsum_bf16_ordered")(ptr(dy), M, N, dy.stride(0), ptr(db), int(accumulate), int(ordered),
-                                         stream_ptr()), "colsum_bf16")
+                                         ptr(scratch), stream_ptr()), "colsum_bf16")
 
 
 def cast_f32_to_bf16(src, dst):
