@@ -24,6 +24,16 @@
 // scores in registers, three Q / dO stages keep two tiles of operands in flight, the dQ of tile
 // i-1 is read out while the products of tile i run.
 //
+// Roles (20 warps): warp 0 issues the TMA copies; warps 1, 2 and 3 each have one thread that issues
+// MMAs (S^T / dP^T and dV; dK; dQ), so that the three products of a tile are issued from three
+// schedulers at once; warps 4-19 do the arithmetic, four per tensor-memory lane quarter with 32
+// query columns each.
+//
+// By-product: the column sums of dK and dV (this kernel's epilogue) and of dQ (the conversion kernel)
+// can be added to an fp32 vector, which is the gradient of the QKV projection's bias.
+// Reproducible form (flash_bwd_ex, ordered): one launch per KV tile, so the additions to the fp32 dQ
+// buffer happen in KV-tile order.
+//
 // This is the hand-written counterpart of what autograd runs for
 // F.scaled_dot_product_attention in the reference (nn/gpt2/modules.py:37, train_ddp.py:141).
 #include "../common/launch.cuh"
