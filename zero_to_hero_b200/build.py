@@ -3,7 +3,7 @@
 `build_all()` compiles every `.cu` / `.cpp` under `csrc/` for sm_100a with nvcc and links
 `zero_to_hero_b200/lib/libz2h.so` (CUDA kernels + C ABI) and `libz2h_host.so` (host-only C++:
 micrograd engine, CPU oracles). nvcc cross-compiles without a GPU, so this also is the
-"does it build" check. Objects are cached under `build/` keyed on source mtimes.
+"does it build" check. Objects are cached under `build/`, named by the content of their source and of all headers.
 
 Run as `python -m zero_to_hero_b200.build [--force] [--verbose] [--bounds]`. `--bounds` builds the
 self-checking debug variant `libz2h_bounds.so` (-DZ2H_BOUNDS, see csrc/common/checked.cuh), which
@@ -42,10 +42,12 @@ def _nvcc() -> str:
 
 
 def _headers_stamp() -> str:
+    """Names the state of all headers by their content (not by path or time, so a copy of the tree on
+    another machine finds the objects that came with it up to date)."""
     h = hashlib.sha1()
     for p in sorted(list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.hpp"))):
-        h.update(str(p).encode())
-        h.update(str(p.stat().st_mtime_ns).encode())
+        h.update(str(p.relative_to(CSRC)).encode())
+        h.update(p.read_bytes())
     return h.hexdigest()[:12]
 
 
@@ -63,27 +65,33 @@ def build_all(force: bool = False, verbose: bool = False, bounds: bool = False) 
     """Compile all native sources; returns {'cuda': path, 'host': path}. `bounds`: the CUDA library
     is built with -DZ2H_BOUNDS into libz2h_bounds.so (the product library is left alone)."""
     nvcc = _nvcc()
-    stamp = _headers_stamp() + ("b" if bounds else "")
+    hdr = _headers_stamp()
+    flavour = "b" if bounds else ""
     extra = ["-DZ2H_BOUNDS"] if bounds else []
+
+    def obj_for(src: Path) -> Path:
+        # the object's name carries the content of its source and of every header: an object that
+        # exists is up to date, whatever the file times say (they do not survive a copy of the tree)
+        tag = hashlib.sha1(hdr.encode() + src.read_bytes()).hexdigest()[:12] + flavour
+        return OBJDIR / src.relative_to(CSRC).with_suffix(f".{tag}.o")
+
     LIBDIR.mkdir(parents=True, exist_ok=True)
     cu_srcs = sorted(p for p in CSRC.rglob("*.cu"))
     host_srcs = sorted(p for p in (CSRC / "cpu").rglob("*.cpp"))
     jobs = []
     cu_objs, host_objs = [], []
     for src in cu_srcs:
-        rel = src.relative_to(CSRC)
-        obj = OBJDIR / rel.with_suffix(f".{stamp}.o")
+        obj = obj_for(src)
         cu_objs.append(obj)
-        if force or not obj.exists() or obj.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        if force or not obj.exists():
             cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, obj, cmd))
     for src in host_srcs:
-        rel = src.relative_to(CSRC)
-        obj = OBJDIR / rel.with_suffix(f".{stamp}.o")
+        obj = obj_for(src)
         host_objs.append(obj)
-        if force or not obj.exists() or obj.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        if force or not obj.exists():
             cmd = ["g++", *CXX_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             jobs.append((src, obj, cmd))
     if jobs:
@@ -109,7 +117,10 @@ def build_all(force: bool = False, verbose: bool = False, bounds: bool = False) 
     out["host"] = host_lib
     # objects of earlier header states are never used again: drop them, keeping both flavours of the
     # current state (the cache otherwise grows by a full set per header edit)
-    keep = {stamp.rstrip("b"), stamp.rstrip("b") + "b"}
+    keep = set()
+    for src in cu_srcs + host_srcs:
+        tag = hashlib.sha1(hdr.encode() + src.read_bytes()).hexdigest()[:12]
+        keep.update({tag, tag + "b"})
     if OBJDIR.exists():
         for old in OBJDIR.rglob("*.o"):
             parts = old.name.split(".")
