@@ -6,6 +6,8 @@ import subprocess
 import sys
 from pathlib import Path
 
+import pytest
+
 ROOT = Path(__file__).resolve().parent.parent
 
 
@@ -58,3 +60,17 @@ def test_check_env_with_mocks():
     assert r.returncode == 1 and "[FAIL] nvcc" in r.stdout
     r = run(m, **{**good, "MOCK_COMPUTE_CAP": "9.0", "MOCK_LIBS_BUILT": "0"})
     assert r.returncode == 0 and r.stdout.count("[warn]") == 2  # not required: building needs no GPU
+
+
+def test_traced_variant_of_a_kernel_builds_and_exports_its_reader():
+    """`utils/kernel_trace.py` compiles a kernel's sources with -DZ2H_KERNEL_TRACE; the marks compile to
+    nothing in the product build, so only this keeps them compiling. CPU: nvcc cross-compiles."""
+    import ctypes
+    import shutil
+    if shutil.which("nvcc") is None and not __import__("pathlib").Path("/usr/local/cuda/bin/nvcc").exists():
+        pytest.skip("no nvcc")
+    from zero_to_hero_b200.utils import kernel_trace
+    lib = kernel_trace.build_trace_lib("flash_bwd")
+    assert isinstance(lib, ctypes.CDLL)
+    assert hasattr(lib, "z2h_flash_bwd_trace_read") and hasattr(lib, "z2h_flash_bwd")
+    assert set(kernel_trace.EPI) >= {"bias", "gelu_save_grad", "mul_aux"}
