@@ -50,7 +50,8 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 using gemm_detail::KernelParams;
 
 
-template <int A_MN, int B_MN>
+// EXTRA: the instantiation that carries the newer epilogue kinds (see epilogue_tile_streamed).
+template <int A_MN, int B_MN, bool EXTRA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB, const KernelParams p) {
@@ -225,9 +226,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       // this warp drains 4 of the 8 column blocks of its 32 rows
       const int c0 = half * 4;
       uint64_t* const tempty = &tempty_bar[acc];
-      gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
+      gemm_detail::epilogue_tile_streamed<EXTRA>(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
                                           smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
-                                          !empty_split, p.split_k > 1 ? sg.kb0 / sched.kb_per_split : 0,
+                                          !empty_split, (EXTRA && p.split_k > 1) ? sg.kb0 / sched.kb_per_split : 0,
                                           [tempty] { mbar_arrive(tempty); });
       if (warp == 2 && lane == 0) Z2H_TRACE();
     }
@@ -259,10 +260,13 @@ int launch(const GemmArgs& g, cudaStream_t stream) {
   KernelParams p = gemm_detail::make_kernel_params(g);
   p.raster_n = gemm_detail::pick_raster_n(g, BM, BN);
 
-  auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
+  auto kern = g.epi >= kEpiGeluSaveGrad ? gemm_bf16_tcgen05_kernel<A_MN, B_MN, true>
+                                        : gemm_bf16_tcgen05_kernel<A_MN, B_MN, false>;
   static std::atomic<unsigned long long> attr_seen{0};
-  if (first_use_on_current_device(attr_seen))
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (first_use_on_current_device(attr_seen)) {
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<A_MN, B_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<A_MN, B_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  }
   const int num_sms = sm_count_current_device();
   const long long tiles = (long long)((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) *
                           (p.stream_k ? (g.K + BK - 1) / BK : p.split_k);

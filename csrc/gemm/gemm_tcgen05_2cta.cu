@@ -47,7 +47,8 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may use");
 // FIXUP: the instantiation that can run stream-K with fix-up (KernelParams::stream_k == 2). Its
 // epilogue needs a warp's whole piece of a tile in registers at once, which costs register spills;
 // the kernels every other launch uses are compiled without that path.
-template <int A_MN, int B_MN, bool FIXUP>
+// EXTRA: the instantiation that carries the newer epilogue kinds (see epilogue_tile_streamed).
+template <int A_MN, int B_MN, bool FIXUP, bool EXTRA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const KernelParams p) {
@@ -226,9 +227,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int c0 = half * 4;
       uint64_t* const tempty = &tempty_bar[acc];
       if (!FIXUP || p.stream_k != 2) {
-        gemm_detail::epilogue_tile_streamed(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
+        gemm_detail::epilogue_tile_streamed<EXTRA>(p, taddr + c0 * 32, row_base + lane, gcol0, sbias, lane,
                                             smem_u32(epi_bias + (warp - 2) * gemm_detail::kEpiBiasFloats),
-                                            !empty_split, p.split_k > 1 ? sg.kb0 / sched.kb_per_split : 0,
+                                            !empty_split, (EXTRA && p.split_k > 1) ? sg.kb0 / sched.kb_per_split : 0,
                                             [tempty] { mbar_arrive_leader_relaxed(tempty); });
         if (warp == 2 && lane == 0) Z2H_TRACE();
         continue;
@@ -386,7 +387,7 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
     const long long tiles_sk = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN);
     const int num_kb = (g.K + BK - 1) / BK;
     const bool plain = p.stream_k == 0 && p.split_k == 1 && g.epi != kEpiAtomicAdd && g.epi != kEpiAccumulate &&
-                       !g.out_fp32;
+                       g.epi < kEpiGeluSaveGrad && !g.out_fp32;  // (the newer kinds have no fix-up instantiation)
     if (plain && fixup_enabled() && tiles_sk >= pairs_avail && num_kb >= 8) {
       const double waves = (double)tiles_sk / pairs_avail;
       const double whole = (double)((tiles_sk + pairs_avail - 1) / pairs_avail);
@@ -402,11 +403,15 @@ int launch_pair(const GemmArgs& g, cudaStream_t stream) {
     }
   }
 
-  auto kern = p.stream_k == 2 ? gemm_bf16_2cta_kernel<A_MN, B_MN, true> : gemm_bf16_2cta_kernel<A_MN, B_MN, false>;
+  const bool extra = g.epi >= kEpiGeluSaveGrad;
+  auto kern = extra ? gemm_bf16_2cta_kernel<A_MN, B_MN, false, true>
+                    : (p.stream_k == 2 ? gemm_bf16_2cta_kernel<A_MN, B_MN, true, false>
+                                       : gemm_bf16_2cta_kernel<A_MN, B_MN, false, false>);
   static std::atomic<unsigned long long> attr_seen{0};
   if (first_use_on_current_device(attr_seen)) {
-    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   }
   const int num_sms = num_sms_all;
   const long long tiles = (long long)((g.M + TM - 1) / TM) * ((g.N + BN - 1) / BN) *
